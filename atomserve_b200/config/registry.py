@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (config.json `architectures[0]`) to its
+"""One registry from an architecture's name (config.json `architectures[0]`, or `architecture`) to its
 configuration class and to the function that turns a configuration into a model
 description (a `ModelSpec`: which parts, in which order, with which tensor names).
 
@@ -49,6 +49,8 @@ def load_model_config(model_dir: str | Path) -> tuple[Architecture, Any]:
 
 def config_from_dict(raw: dict) -> tuple[Architecture, Any]:
     names = raw.get("architectures") or []
+    if not names and isinstance(raw.get("architecture"), str):
+        names = [raw["architecture"]]  # the one-name form of the key
     if len(names) != 1:
         raise ModelConfigError(f"config.json must name exactly one architecture, got {names}")
     arch = architecture_for(names[0])
@@ -57,4 +59,4 @@ def config_from_dict(raw: dict) -> tuple[Architecture, Any]:
 
 def _ensure_builtin() -> None:
     if "Qwen3ForCausalLM" not in _ARCHITECTURES:
-        from atomserve_b200.models import qwen3  # noqa: F401  (registers itself)
+        from atomserve_b200.models import gefilix, qwen3  # noqa: F401  (register themselves)

@@ -28,7 +28,7 @@ from atomserve_b200.engine.runner import ModelRunner, Row
 from atomserve_b200.ops import require_device
 from atomserve_b200.weights.loader import load_model, parse_dtype
 
-MAX_LIVE_REQUESTS = 8
+MAX_LIVE_REQUESTS = 4
 
 
 class TraceReplayer:

@@ -47,6 +47,25 @@ _SIGNATURES = {
     "asb_argmax_rows": [_P, _P, _I, _I, _P],
     "asb_presence_penalty": [_P, _P, _P, _P, _I, _I, _P],
     "asb_sample_rows": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P],
+    # a float32 residual stream with the norm after the sum
+    "asb_embedding_scaled": [_P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
+    "asb_cast_rows": [_P, _P, ctypes.c_longlong, _I, _P],
+    "asb_scaled_add_rmsnorm": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _F, _F, _I, _P],
+    "asb_gated_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _I, _P],
+    "asb_gelu": [_P, _P, ctypes.c_longlong, _I, _I, _P],
+    "asb_clamped_glu": [_P, _P, _I, _I, _F, _F, _F, _I, _P],
+    # linear attention with a decay per head
+    "asb_lightning_attention": [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    # attention over a cached latent
+    "asb_latent_prepare": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "asb_head_matmul": [_P, _I, _I, _I, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "asb_latent_attention": [_P] * 9 + [_I] * 9 + [_F, _I, _P],
+    # routed experts
+    "asb_moe_route": [_P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _P],
+    "asb_moe_group": [_P, _I, _I, _I, _P, _P, _P, _P],
+    "asb_moe_glu": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _F, _I, _P],
+    "asb_moe_down": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "asb_moe_combine": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
 }
 
 
@@ -75,6 +94,8 @@ def lib() -> ctypes.CDLL:
         handle.asb_set_pdl(int(os.environ.get("ATOMSERVE_B200_PDL", "1") != "0"))
         handle.asb_attention_tile_shape.argtypes = [c_int, c_void_p, c_void_p]
         handle.asb_attention_tile_shape.restype = None
+        handle.asb_latent_attention_tile_shape.argtypes = [c_int, c_void_p, c_void_p]
+        handle.asb_latent_attention_tile_shape.restype = None
         for name, argtypes in _SIGNATURES.items():
             fn = getattr(handle, name, None)
             if fn is None:

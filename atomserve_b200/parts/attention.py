@@ -80,6 +80,8 @@ class GQAttention(Mixer):
         # the position encoding says how it is applied: by the fused kernel below (a rotation by
         # position x frequency), or by its own `encode` on the normalised queries and keys
         rotary = self.position.fused_rotary() if self.position is not None else None
+        if rotary is not None and rotary.pairing != "half":
+            raise NotImplementedError("this attention's fused kernel turns pairs (i, i + rotary_dim / 2) only")
         if self.position is not None and rotary is None:
             q = self._project_encode_store(h, ctx, cache, write_cache)
         else:

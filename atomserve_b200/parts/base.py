@@ -152,11 +152,13 @@ class Norm(Part):
 @dataclass(frozen=True)
 class FusedRotary:
     """An encoding that a mixer's fused kernel can apply by itself: each head's first
-    `rotary_dim` dimensions are turned, pair (i, i + rotary_dim / 2) by the angle
-    position * inv_freq[i] (`inv_freq`: float32 [rotary_dim / 2] on the device)."""
+    `rotary_dim` dimensions are turned, pair i by the angle position * inv_freq[i] (`inv_freq`:
+    float32 [rotary_dim / 2] on the device). `pairing` says which entries make pair i: "half",
+    (i, i + rotary_dim / 2), or "interleaved", (2i, 2i + 1)."""
 
     inv_freq: torch.Tensor
     rotary_dim: int
+    pairing: str = "half"
 
 
 class PositionEncoding(Part):
@@ -281,4 +283,4 @@ def build_block(kind: str, mixer: Mixer, feed_forward: FeedForward, mixer_norm: 
 
 def _ensure_builtin() -> None:
     if "rms_norm" not in _REGISTRIES["norm"]:
-        from atomserve_b200.parts import attention, block, embedding, mlp, norms, rotary  # noqa: F401
+        from atomserve_b200.parts import attention, block, embedding, experts, latent_attention, lightning, mlp, norms, rotary  # noqa: F401

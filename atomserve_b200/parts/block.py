@@ -6,6 +6,7 @@ from __future__ import annotations
 
 import torch
 
+from atomserve_b200 import ops
 from atomserve_b200.parts.base import Block, CacheView, Norm, StepContext, register_part
 
 
@@ -26,4 +27,37 @@ class PreNormBlock(Block):
         return self.feed_forward.forward_then(normed, x, ctx, then)
 
 
+class PostNormBlock(Block):
+    """The arrangement with the norm after the sum, over a float32 residual stream:
+    x <- norm1(alpha x + mixer(x)); x <- norm2(alpha x + ff(x)), the sublayers reading x itself
+    (in the compute dtype). The norms are `StreamRMSNorm`s and carry alpha. A layer without a
+    feed-forward (kind "none") ends after its first half. In a run of blocks the compute-dtype copy
+    of x travels in the place where pre-norm blocks hand on the next block's normed input."""
+
+    dtype = torch.float32  # the compute dtype, told by `bind_dtype` once the weights are loaded
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        super().load(tensors)
+        self.has_feed_forward = not getattr(self.feed_forward, "absent", False)
+
+    def bind_dtype(self, dtype: torch.dtype) -> None:
+        self.dtype = dtype
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if hasattr(norm, "bind_dtype"):
+                norm.bind_dtype(dtype)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView | None,
+                write_cache: bool = True) -> torch.Tensor:  # fmt: skip
+        return self.forward_chain(x, None, ctx, cache, write_cache, None)[0]
+
+    def forward_chain(self, x: torch.Tensor, normed: torch.Tensor | None, ctx: StepContext, cache: CacheView | None,
+                      write_cache: bool, then: Norm | None) -> tuple[torch.Tensor, torch.Tensor | None]:  # fmt: skip
+        h = normed if normed is not None else ops.cast_rows(x, self.dtype)
+        x, h = self.mixer_norm.add_forward(x, self.mixer.forward(h, None, ctx, cache, write_cache))
+        if self.has_feed_forward:
+            x, h = self.feed_forward_norm.add_forward(x, self.feed_forward.forward(h, None, ctx))
+        return x, h
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "post_norm", PostNormBlock)

@@ -12,8 +12,8 @@ from atomserve_b200.parts.spec import TensorSpec
 
 
 class TokenEmbedding(Part):
-    def __init__(self, hidden_size: int, prefix: str, vocab_size: int):
-        self.hidden_size, self.vocab_size, self.name = hidden_size, vocab_size, prefix + "weight"
+    def __init__(self, hidden_size: int, prefix: str, vocab_size: int, tensor: str | None = None):
+        self.hidden_size, self.vocab_size, self.name = hidden_size, vocab_size, tensor or prefix + "weight"
         self.table: torch.Tensor | None = None
         self.status: torch.Tensor | None = None
 
@@ -30,9 +30,21 @@ class TokenEmbedding(Part):
         return ops.embedding(token_ids, self.table, self.status)
 
 
+class ScaledEmbedding(TokenEmbedding):
+    """table[token] * scale as float32: the start of a residual stream that is kept in float32
+    whatever the compute dtype."""
+
+    def __init__(self, hidden_size: int, prefix: str, vocab_size: int, scale: float = 1.0, tensor: str | None = None):
+        super().__init__(hidden_size, prefix, vocab_size, tensor)
+        self.scale = float(scale)
+
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        return ops.embedding_scaled(token_ids, self.table, self.scale, self.status)
+
+
 class LMHead(Part):
-    def __init__(self, hidden_size: int, prefix: str, vocab_size: int, tied: bool):
-        self.hidden_size, self.vocab_size, self.tied, self.name = hidden_size, vocab_size, tied, prefix + "weight"
+    def __init__(self, hidden_size: int, prefix: str, vocab_size: int, tied: bool, tensor: str | None = None):
+        self.hidden_size, self.vocab_size, self.tied, self.name = hidden_size, vocab_size, tied, tensor or prefix + "weight"
         self.weight: torch.Tensor | None = None
 
     def tensor_specs(self) -> list[TensorSpec]:
@@ -50,4 +62,5 @@ class LMHead(Part):
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("embedding", "scaled_embedding", ScaledEmbedding)
 register_part("head", "lm_head", LMHead)

@@ -58,6 +58,10 @@ class DecoderModel:
             self.head.tie(self.embedding)
         self.dtype = self.embedding.table.dtype
         self.device = self.embedding.table.device
+        for part in self.parts():  # parts that compute in one dtype and keep another (a float32 stream)
+            bind = getattr(part, "bind_dtype", None)
+            if bind is not None:
+                bind(self.dtype)
 
     def cache_requirements(self) -> list[tuple[PageSpec | None, list[StateSpec]]]:
         """For each entry of the run order: the pages and state it owns (none if it reads

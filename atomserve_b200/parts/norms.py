@@ -11,10 +11,10 @@ from atomserve_b200.parts.spec import TensorSpec
 
 
 class RMSNorm(Norm):
-    def __init__(self, hidden_size: int, prefix: str, eps: float, width: int | None = None):
+    def __init__(self, hidden_size: int, prefix: str, eps: float, width: int | None = None, tensor: str | None = None):
         self.width = width or hidden_size
         self.eps = float(eps)
-        self.name = prefix + "weight"
+        self.name = tensor or prefix + "weight"
         self.gain: torch.Tensor | None = None
 
     def tensor_specs(self) -> list[TensorSpec]:
@@ -39,4 +39,38 @@ class RMSNorm(Norm):
         return total, self.forward(total)
 
 
+class StreamRMSNorm(RMSNorm):
+    """RMSNorm of a residual stream that is kept in float32 whatever the compute dtype, for
+    blocks whose norm follows the sum: `add_forward(x, y)` is norm(alpha x + y), returned both as
+    the new float32 stream and in the compute dtype (what the next products read); `forward` is
+    the plain norm of (rows of) the stream in the compute dtype, as a final norm before the head."""
+
+    def __init__(self, hidden_size: int, prefix: str, eps: float, alpha: float = 1.0, width: int | None = None,
+                 tensor: str | None = None):  # fmt: skip
+        super().__init__(hidden_size, prefix, eps, width, tensor)
+        self.alpha = float(alpha)
+        self.dtype = torch.float32
+
+    def bind_dtype(self, dtype: torch.dtype) -> None:
+        self.dtype = dtype
+
+    def forward(self, x: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
+        return ops.scaled_add_rms_norm(x, None, 1.0, self.gain, self.eps, self.dtype, rows, want_stream=False)[1]
+
+    def add_forward(self, x: torch.Tensor, y: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        return ops.scaled_add_rms_norm(x, y, self.alpha, self.gain, self.eps, self.dtype)
+
+
+class NoNorm(Norm):
+    """The norm of a sublayer that a layer does not have."""
+
+    def __init__(self, hidden_size: int, prefix: str):
+        pass
+
+    def forward(self, x: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
+        raise RuntimeError("this layer has no such norm")
+
+
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "stream_rms_norm", StreamRMSNorm)
+register_part("norm", "none", NoNorm)
