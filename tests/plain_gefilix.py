@@ -220,3 +220,15 @@ def random_checkpoint(cfg, seed, matrix_std=None, bf16_exact=True):
             if bf16_exact:
                 w[name] = w[name].bfloat16().float()
     return w
+
+
+def greedy_generate(w, cfg, prompt, n, dtype=torch.float64):
+    """The n tokens that follow `prompt` when the largest logit is taken each time."""
+    w = {k: v.to(dtype) for k, v in w.items()}
+    carried, out = {}, []
+    logits = forward(w, cfg, prompt, dtype, 0, carried)
+    for i in range(n):
+        out.append(int(logits[-1].argmax()))
+        if i + 1 < n:
+            logits = forward(w, cfg, out[-1:], dtype, len(prompt) + i, carried)
+    return out
