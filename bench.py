@@ -503,6 +503,158 @@ def gemm_timelines(which: str, tokens: list[int]) -> None:
         del ws
 
 
+# ---- the Gefilix design beside Qwen3 at equal width (`--only designs`) ---------------------------
+
+def gefilix_shape(width: int, layers: int) -> dict:
+    """Layer sizes that resemble a served model's: heads of 128, a latent of 512 + 64, experts a
+    quarter of the width's usual feed-forward each. Layers alternate lightning and latent attention
+    (every second latent layer reading the first one's cache), experts everywhere but layer 0."""
+    heads = width // 128
+    moe = dict(kind="moe", expert=dict(ff=width // 2, limit=7.0),
+               router=dict(experts=32, top=4, scale=2.5, groups=dict(count=4, keep=2)), shared=dict(ff=width, limit=7.0))
+    out, first_latent = [], None
+    for i in range(layers):
+        if i % 2 == 0:
+            mixer = dict(type="lightning", mixer=dict(heads=heads, dim=128, vdim=128, decay=[1.0 - 2.0 ** -(2 + h % 8) for h in range(heads)]))
+        else:
+            m = dict(heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=512, scale=192 ** -0.5, rot=dict(base=10000.0, dims=64))
+            if first_latent is None:
+                first_latent = i
+            elif (i // 2) % 2:
+                m["kv_from"] = first_latent
+            mixer = dict(type="latent_attention", mixer=m)
+        out.append(dict(mixer, mlp=dict(kind="dense", ff=3 * width) if i == 0 else moe))
+    return dict(architecture="Gefilix", vocab=32000, width=width, layers=out, norm=dict(eps=1e-6), postln_alpha=1.0,
+                embedding=dict(scale=1.0))
+
+
+def time_designs(widths: list[int], layers: int, steps: int, warmup: int, pk: dict) -> None:
+    """Prefill and decode of a Gefilix model and of a Qwen3 model of the same width and depth
+    (random weights), through the step function, and the design's own kernels one by one against
+    their rooflines beside the like kernels of Qwen3."""
+    import torch
+
+    from atomserve_b200 import ops
+    from atomserve_b200.config import EngineConfig
+    from atomserve_b200.config.registry import config_from_dict
+    from atomserve_b200.engine.engine import create_engine
+    from atomserve_b200.engine.runner import Row
+    from atomserve_b200.weights import random_model
+
+    def timed(fn, n=steps):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(n):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / n
+
+    def model_times(raw, vocab):
+        _, config = config_from_dict(raw)
+        model = random_model(config, seed=0, dtype="bfloat16", device="cuda")
+        context = PROMPT_TOKENS + 256
+        engine = create_engine(model, EngineConfig(block_size=BLOCK_SIZE, num_blocks=66 * (context // BLOCK_SIZE), max_num_seqs=64,
+                                                   max_num_batched_tokens=PROMPT_TOKENS, max_model_len=context,
+                                                   enable_prefix_caching=False), sampler_seed=0)  # fmt: skip
+        runner, cache = engine.runner, engine.runner.cache
+        out = {}
+        rc = cache.new_request()
+        assert cache.admit(rc) and cache.reserve(rc, 0, PROMPT_TOKENS)
+        row = [Row([t % vocab for t in prompts(1, PROMPT_TOKENS)[0]], 0, rc, [PROMPT_TOKENS - 1])]
+        ms = timed(lambda: runner.step(row), max(steps // 4, 4))
+        out["prefill_2048"] = {"ms": round(ms, 3), "tokens_per_s": round(PROMPT_TOKENS * 1000 / ms, 1)}
+        cache.free(rc)
+        for batch in (8, 64):
+            reqs = []
+            for p in prompts(batch, PROMPT_TOKENS):
+                rc = cache.new_request()
+                assert cache.admit(rc) and cache.reserve(rc, 0, PROMPT_TOKENS + 1)
+                runner.step([Row([t % vocab for t in p], 0, rc, [])])
+                reqs.append(rc)
+            rows = [Row([(7 + 13 * i) % vocab], PROMPT_TOKENS, rc, [0]) for i, rc in enumerate(reqs)]
+            ms = timed(lambda: ops.argmax_rows(runner.step(rows)))
+            out[f"decode_b{batch}"] = {"ms": round(ms, 4), "tokens_per_s": round(batch * 1000 / ms, 1)}
+            for rc in reqs:
+                cache.free(rc)
+        del engine, model
+        torch.cuda.empty_cache()
+        return out
+
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")  # noqa: E731
+    bw, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    for width in widths:
+        raw = gefilix_shape(width, layers)
+        heads = width // 128
+        qwen = {**QWEN3_8B, "vocab_size": 32000, "hidden_size": width, "intermediate_size": 3 * width,
+                "num_hidden_layers": layers, "num_attention_heads": heads, "num_key_value_heads": max(heads // 4, 1)}
+        line = {"only": "designs", "width": width, "layers": layers, "peaks": pk["source"],
+                "gefilix": model_times(raw, 32000), "qwen3": model_times(qwen, 32000)}
+        # -- kernels alone: time, the bytes or FLOPs they must move, and the fraction of the measured peak
+        kern = {}
+        T, B, ctx = PROMPT_TOKENS, 64, PROMPT_TOKENS
+        H, D, R, Rt, bs = heads, 128, 512, 64, BLOCK_SIZE
+        bf = torch.bfloat16
+        # lightning attention: prefill (one request of T tokens) and decode (B requests, one token)
+        proj = torch.randn(T, 4 * H * D, device="cuda", dtype=bf)
+        state = torch.zeros(B, H, D, D, device="cuda")
+        decay = torch.full((H,), 0.99, device="cuda")
+        ms = timed(lambda: ops.lightning_attention(proj, 0, H * D, 2 * H * D, state, i32([0]), i32([0, T]), decay, 1))
+        kern["lightning_prefill"] = {"ms": round(ms, 4), "gflops": round(4.0 * T * H * D * D / ms / 1e6, 1), "note": "float32 CUDA cores"}
+        ms = timed(lambda: ops.lightning_attention(proj[:B], 0, H * D, 2 * H * D, state, i32(list(range(B))), i32(list(range(B + 1))), decay, B))
+        kern["lightning_decode_b64"] = {"ms": round(ms, 4), "hbm_frac": round(2.0 * B * H * D * D * 4 / (ms * 1e-3) / bw, 3)}
+        # latent attention beside the paged attention of Qwen3: decode at batch B, context ctx
+        pages_per = ctx // bs
+        tables = i32([[r * pages_per + j for j in range(pages_per)] for r in range(B)])
+        lat_pages = torch.randn(B * pages_per, 1, bs, R + Rt, device="cuda", dtype=bf)
+        q_lat = torch.randn(B, H, R + Rt, device="cuda")
+        starts, at = i32(list(range(B + 1))), i32([ctx - 1] * B)
+        ms = timed(lambda: ops.latent_attention(q_lat, lat_pages, tables, starts, at, rank=R, num_requests=B, max_context=ctx, scale=0.07))
+        kern["latent_attention_decode_b64"] = {"ms": round(ms, 4), "hbm_frac": round(B * ctx * (R + Rt) * 2 / (ms * 1e-3) / bw, 3)}
+        KV = max(H // 4, 1)
+        k_pages = torch.randn(B * pages_per, KV, bs, 128, device="cuda", dtype=bf)
+        v_pages = torch.randn_like(k_pages)
+        q = torch.randn(B, H, 128, device="cuda", dtype=bf)
+        ms = timed(lambda: ops.paged_attention(q, k_pages, v_pages, tables, starts, at, num_requests=B, max_context=ctx, window=None,
+                                               scale=0.088, host_q_lens=[1] * B))  # fmt: skip
+        kern["paged_attention_decode_b64"] = {"ms": round(ms, 4), "hbm_frac": round(2.0 * B * ctx * KV * 128 * 2 / (ms * 1e-3) / bw, 3)}
+        # prefill attention: one request of T tokens
+        q_lat = torch.randn(T, H, R + Rt, device="cuda")
+        t1 = i32([list(range(pages_per))])
+        ms = timed(lambda: ops.latent_attention(q_lat, lat_pages, t1, i32([0, T]), i32([0]), rank=R, num_requests=1, max_context=T, scale=0.07), 4)
+        kern["latent_attention_prefill"] = {"ms": round(ms, 3), "tc_frac": round(2.0 * T * T / 2 * H * (2 * R + Rt) / (ms * 1e-3) / tf, 4)}
+        q = torch.randn(T, H, 128, device="cuda", dtype=bf)
+        ms = timed(lambda: ops.paged_attention(q, k_pages, v_pages, t1, i32([0, T]), i32([0]), num_requests=1, max_context=T, window=None,
+                                               scale=0.088, host_q_lens=[T]))  # fmt: skip
+        kern["paged_attention_prefill"] = {"ms": round(ms, 3), "tc_frac": round(4.0 * T * T / 2 * H * 128 / (ms * 1e-3) / tf, 4)}
+        # experts: the grouped products beside a dense SwiGLU of the same active size
+        E, top, F = 32, 4, width // 2
+        gate = torch.randn(E, F, width, device="cuda", dtype=bf) * 0.02
+        up, down = torch.randn_like(gate) * 0.02, torch.randn(E, width, F, device="cuda", dtype=bf) * 0.02
+        for name, n in (("prefill", T), ("decode_b64", B)):
+            x = torch.randn(n, width, device="cuda", dtype=bf)
+            ids = torch.stack([torch.randperm(E, device="cuda")[:top] for _ in range(n)]).int()
+            offsets, row_token, pair_row = ops.group_by_expert(ids, E)
+
+            def experts():
+                hidden = ops.experts_glu(x, row_token, offsets, gate, up, 7.0, 1.702, 1.0)
+                return ops.experts_down(hidden, offsets, down)
+
+            ms = timed(experts, 4 if n == T else steps)
+            flops, weights = 6.0 * n * top * F * width, 3.0 * min(E, n * top) * F * width * 2
+            kern[f"experts_{name}"] = {"ms": round(ms, 4), "tc_frac": round(flops / (ms * 1e-3) / tf, 4), "hbm_frac": round(weights / (ms * 1e-3) / bw, 3)}
+            w_gu = torch.randn(2 * top * F, width, device="cuda", dtype=bf) * 0.02
+            w_d = torch.randn(width, top * F, device="cuda", dtype=bf) * 0.02
+            ms = timed(lambda: ops.linear(ops.linear_swiglu(x, w_gu), w_d), 4 if n == T else steps)
+            kern[f"dense_swiglu_{name}"] = {"ms": round(ms, 4), "tc_frac": round(flops / (ms * 1e-3) / tf, 4),
+                                            "hbm_frac": round(3.0 * top * F * width * 2 / (ms * 1e-3) / bw, 3)}  # fmt: skip
+        line["kernels"] = kern
+        print(json.dumps(line), flush=True)
+
+
 def reference_arm(args) -> int:
     """The same measurement on the unmodified reference (baseline/reference_arm.py): its own
     engine, sampler and PyTorch model code on this GPU, nothing of this package."""
@@ -558,7 +710,7 @@ def main() -> int:
                         help="fewer layers than the model has (same layer sizes), where time or memory needs it")  # fmt: skip
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--only", choices=["decode", "prefill", "gemm", "serve", "attention", "sampling"], help="time just this (for profiling small cases and the other shapes)")
+    parser.add_argument("--only", choices=["decode", "prefill", "gemm", "serve", "attention", "sampling", "designs"], help="time just this (for profiling small cases and the other shapes)")
     parser.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="with --only decode/prefill/serve: layer sizes of Qwen3-8B, -14B or -32B")
     parser.add_argument("--context", type=int, default=PROMPT_TOKENS, help="with --only decode: tokens each request holds when decoding starts")
     parser.add_argument("--requests", type=int, default=32, help="with --only serve: requests submitted at once")
@@ -566,6 +718,7 @@ def main() -> int:
     parser.add_argument("--budget", type=int, default=512, help="with --only serve: the scheduler's token budget per step")
     parser.add_argument("--gemm-shape", default="all", help="with --only gemm: qkv, o, gate_up, down, lm_head or all")
     parser.add_argument("--gemm-tokens", default="1,8,64,2048", help="with --only gemm: token counts, comma-separated")
+    parser.add_argument("--widths", default="2048,4096", help="with --only designs: model widths, comma-separated")
     parser.add_argument("--timeline", action="store_true", help="with --only gemm: where a decode-size call's time goes")
     args = parser.parse_args()
     args.layers_given = any(a == "--layers" or a.startswith("--layers=") for a in sys.argv[1:])
@@ -587,6 +740,9 @@ def main() -> int:
         return 0
     if args.only == "sampling":
         time_sampling([1, 8, 64], SHAPES[args.shape]["vocab_size"])
+        return 0
+    if args.only == "designs":
+        time_designs([int(w) for w in args.widths.split(",")], args.layers if args.layers_given else 4, max(args.steps // 4, 8), warmup, pk)
         return 0
     if args.only == "gemm" and args.timeline:
         gemm_timelines(args.gemm_shape, [int(t) for t in args.gemm_tokens.split(",")])
