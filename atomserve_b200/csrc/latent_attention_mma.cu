@@ -1,0 +1,320 @@
+// Attention over a cached latent on the tensor cores, for bfloat16 pages: what
+// asb_latent_attention (latent_attention.cu, the float32 path and the fallback) computes, with
+// Q K^T and P V as mma.sync m16n8k16 (bfloat16 in, float32 accumulate).
+//
+// A block owns 32 (token, head) rows, the heads of one or a few neighbouring tokens of a
+// request, which all read the same keys: one shared key head of width Dk = rank + rot, whose
+// first `rank` entries are also the values. Per tile of 64 keys, staged once in shared memory:
+//   1. each of the 8 warps multiplies the 32 query rows with 8 of the keys (k over Dk) and
+//      writes the scaled, masked float32 scores to shared memory;
+//   2. each warp runs the online softmax of 4 of the rows: running maximum and sum in float32,
+//      the weights written as bfloat16, the factor by which older sums shrink kept per row;
+//   3. each warp multiplies the 32 x 64 weights with the keys' first `rank` columns for its own
+//      eighth of the output columns (the keys read through ldmatrix.trans as the B operand).
+// Scores, maxima, sums and the output accumulators are float32; the queries and the softmax
+// weights enter the tensor cores rounded to bfloat16. Key partitions, their alignment to
+// absolute positions and the partial results are those of the CUDA-core kernel, merged by
+// asb_attention_reduce.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MR = 32;   // rows a block
+constexpr int KT = 64;   // keys a tile
+constexpr int kWarps = 8;
+constexpr int LDS = KT + 1;  // float32 scores
+constexpr int LDP = KT + 8;  // bfloat16 weights
+
+struct LatentParams {
+  const float* q;            // [T, H, Dk]
+  float* out;                // [T, H, rank]
+  const __nv_bfloat16* pages;  // [num_blocks, 1, bs, Dk]
+  const int* block_tables;
+  const int* req_q_start;
+  const int* req_pos_start;
+  float* part_m;
+  float* part_l;
+  float* part_acc;
+  int R, H, rank, Dk, DKP, LDK, bs, table_width;
+  int QT, GC, HC;
+  int PS, NP;
+  float scale;
+};
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t (&b)[2], const void* row) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b[0]), "=r"(b[1]) : "r"(addr));
+}
+
+// NT: 8-column tiles of the output per warp; the block covers 64 * NT >= rank columns
+template <int NT>
+__global__ void __launch_bounds__(kWarps * 32)
+latent_attention_mma_kernel(const LatentParams p) {
+  asb::pdl_wait();
+  asb::pdl_launch_dependents();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int Dk = p.Dk, Dv = p.rank, DKP = p.DKP, LDK = p.LDK;
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [MR][LDK]
+  __nv_bfloat16* k_s = q_s + MR * LDK;                               // [KT][LDK] (+ slack the launcher adds)
+  __nv_bfloat16* p_s = k_s + (KT + 1) * LDK;                         // [MR][LDP]
+  float* s_s = reinterpret_cast<float*>(p_s + MR * LDP);             // [MR][LDS]
+  float* row_m = s_s + MR * LDS;                                     // [MR]
+  float* row_l = row_m + MR;
+  float* row_c = row_l + MR;
+  __shared__ int block_of_key[KT];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+
+  int tile = blockIdx.x, r = 0, q_len = 0;
+  for (; r < p.R; ++r) {
+    q_len = p.req_q_start[r + 1] - p.req_q_start[r];
+    const int tiles = (q_len + p.QT - 1) / p.QT;
+    if (tile < tiles) break;
+    tile -= tiles;
+  }
+  if (r == p.R) return;
+  const int q0 = tile * p.QT;
+  const int nq = min(p.QT, q_len - q0);
+  const int row0 = p.req_q_start[r] + q0;
+  const int pos0 = p.req_pos_start[r] + q0;
+  const int head0 = blockIdx.y * p.GC;
+  const int gc = min(p.GC, p.H - head0);
+  const int num_rows = nq * gc;  // row rr = qi * gc + g
+  const int hi = pos0 + nq;
+  const int key_lo = blockIdx.z * p.PS;
+  const int key_hi = (int)min((long long)hi, (long long)(blockIdx.z + 1) * p.PS);
+
+  // queries as bfloat16, rows beyond the block's and columns beyond Dk zero
+  for (int i = threadIdx.x; i < MR * LDK; i += blockDim.x) {
+    const int rr = i / LDK, e = i - rr * LDK;
+    float v = 0.f;
+    if (rr < num_rows && e < Dk) {
+      const int qi = rr / gc, gg = rr - qi * gc;
+      v = p.q[((size_t)(row0 + qi) * p.H + head0 + gg) * Dk + e];
+    }
+    q_s[i] = __float2bfloat16_rn(v);
+  }
+  // the key tile's columns beyond Dk, and the slack behind it, stay zero
+  for (int i = threadIdx.x; i < (KT + 1) * LDK; i += blockDim.x) k_s[i] = __float2bfloat16_rn(0.f);
+  if (threadIdx.x < MR) {
+    row_m[threadIdx.x] = -INFINITY;
+    row_l[threadIdx.x] = 0.f;
+  }
+  float acc[2][NT][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
+
+  const int* table = p.block_tables + (size_t)r * p.table_width;
+  const bool vector = (Dk % 8 == 0) && (((uintptr_t)p.pages & 15) == 0);
+  const int chunks = Dk / 8;
+
+  for (int kt0 = (key_lo / KT) * KT; kt0 < key_hi; kt0 += KT) {
+    __syncthreads();  // the previous tile's keys and weights have been read
+    if (threadIdx.x < KT) {
+      const int j = kt0 + threadIdx.x;
+      block_of_key[threadIdx.x] = (j >= key_lo && j < key_hi) ? table[j / p.bs] : -1;
+    }
+    __syncthreads();
+    if (vector) {
+      for (int i = threadIdx.x; i < KT * chunks; i += blockDim.x) {
+        const int jj = i / chunks, c = i - jj * chunks;
+        const int blk = block_of_key[jj];
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (blk >= 0) v = *reinterpret_cast<const uint4*>(p.pages + ((size_t)blk * p.bs + (kt0 + jj) % p.bs) * Dk + c * 8);
+        *reinterpret_cast<uint4*>(k_s + jj * LDK + c * 8) = v;
+      }
+    } else {
+      for (int i = threadIdx.x; i < KT * Dk; i += blockDim.x) {
+        const int jj = i / Dk, e = i - jj * Dk;
+        const int blk = block_of_key[jj];
+        k_s[jj * LDK + e] = blk >= 0 ? p.pages[((size_t)blk * p.bs + (kt0 + jj) % p.bs) * Dk + e] : __float2bfloat16_rn(0.f);
+      }
+    }
+    __syncthreads();
+
+    // 1. scores of the 32 rows against this warp's 8 keys
+    {
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      const __nv_bfloat16* kb = k_s + (warp * 8 + g) * LDK;
+      for (int kk = 0; kk < DKP; kk += 16) {
+        uint32_t b[2];
+        b[0] = *reinterpret_cast<const uint32_t*>(kb + kk + 2 * t);
+        b[1] = *reinterpret_cast<const uint32_t*>(kb + kk + 2 * t + 8);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const __nv_bfloat16* qa = q_s + (i * 16 + g) * LDK + kk + 2 * t;
+          uint32_t a[4];
+          a[0] = *reinterpret_cast<const uint32_t*>(qa);
+          a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * LDK);
+          a[2] = *reinterpret_cast<const uint32_t*>(qa + 8);
+          a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * LDK + 8);
+          mma_bf16(s[i], a, b);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int rr = i * 16 + g + (c >> 1) * 8;
+          const int jj = warp * 8 + 2 * t + (c & 1);
+          const int j = kt0 + jj;
+          const bool visible = rr < num_rows && block_of_key[jj] >= 0 && j <= pos0 + rr / gc;
+          s_s[rr * LDS + jj] = visible ? s[i][c] * p.scale : -INFINITY;
+        }
+    }
+    __syncthreads();
+
+    // 2. online softmax, 4 rows a warp, two keys a lane
+#pragma unroll
+    for (int u = 0; u < MR / kWarps; ++u) {
+      const int rr = warp * (MR / kWarps) + u;
+      const float s0 = s_s[rr * LDS + lane], s1 = s_s[rr * LDS + lane + 32];
+      const float m_old = row_m[rr];
+      const float m_new = fmaxf(m_old, asb::warp_max(fmaxf(s0, s1)));
+      float p0 = 0.f, p1 = 0.f, corr = 1.f;
+      if (m_new != -INFINITY) {
+        p0 = expf(s0 - m_new);
+        p1 = expf(s1 - m_new);
+        corr = expf(m_old - m_new);
+      }
+      const float sum = asb::warp_sum(p0 + p1);
+      p_s[rr * LDP + lane] = __float2bfloat16_rn(p0);
+      p_s[rr * LDP + lane + 32] = __float2bfloat16_rn(p1);
+      if (lane == 0) {
+        row_m[rr] = m_new;
+        row_l[rr] = row_l[rr] * corr + sum;
+        row_c[rr] = corr;
+      }
+    }
+    __syncthreads();
+
+    // 3. the weighted sum of the keys' value columns, this warp's columns
+    {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const float c_lo = row_c[i * 16 + g], c_hi = row_c[i * 16 + g + 8];
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          acc[i][j][0] *= c_lo;
+          acc[i][j][1] *= c_lo;
+          acc[i][j][2] *= c_hi;
+          acc[i][j][3] *= c_hi;
+        }
+      }
+      const int col0 = warp * NT * 8;
+#pragma unroll
+      for (int kk = 0; kk < KT; kk += 16) {
+        uint32_t a[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const __nv_bfloat16* pa = p_s + (i * 16 + g) * LDP + kk + 2 * t;
+          a[i][0] = *reinterpret_cast<const uint32_t*>(pa);
+          a[i][1] = *reinterpret_cast<const uint32_t*>(pa + 8 * LDP);
+          a[i][2] = *reinterpret_cast<const uint32_t*>(pa + 8);
+          a[i][3] = *reinterpret_cast<const uint32_t*>(pa + 8 * LDP + 8);
+        }
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          uint32_t b[2];
+          ldmatrix_x2_trans(b, k_s + (kk + (lane & 15)) * LDK + col0 + j * 8);
+          mma_bf16(acc[0][j], a[0], b);
+          mma_bf16(acc[1][j], a[1], b);
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int rr = i * 16 + g + half * 8;
+      if (rr >= num_rows) continue;
+      const int qi = rr / gc, gg = rr - qi * gc;
+      const size_t row = (size_t)(row0 + qi) * p.H + head0 + gg;
+      const float l = row_l[rr];
+      if (p.NP > 1 && warp == 0 && t == 0) {
+        p.part_m[row * p.NP + blockIdx.z] = row_m[rr];
+        p.part_l[row * p.NP + blockIdx.z] = l;
+      }
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int col = warp * NT * 8 + j * 8 + 2 * t + c;
+          if (col >= Dv) continue;
+          const float v = acc[i][j][half * 2 + c];
+          if (p.NP == 1) p.out[row * Dv + col] = v / l;
+          else p.part_acc[(row * p.NP + blockIdx.z) * Dv + col] = v;
+        }
+    }
+}
+
+template <int NT>
+int launch_attention(const LatentParams& p, int num_tokens, size_t smem, cudaStream_t stream) {
+  auto kern = latent_attention_mma_kernel<NT>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return asb::fail("latent_attention_mma: shared memory %zu: %s", smem, cudaGetErrorString(e));
+  dim3 grid((num_tokens + p.QT - 1) / p.QT + p.R, p.HC, p.NP);
+  asb::launch(kern, grid, kWarps * 32, smem, stream, p);
+  return asb::check_launch("latent_attention_mma");
+}
+
+size_t smem_bytes(int LDK) {
+  return sizeof(__nv_bfloat16) * ((size_t)(MR + KT + 1) * LDK + MR * LDP) + sizeof(float) * (MR * LDS + 3 * MR);
+}
+
+int padded_key_stride(int rank, int rot) {
+  const int dkp = (rank + rot + 15) / 16 * 16;
+  int nt = 1;
+  while (64 * nt < rank) nt <<= 1;
+  const int widest = dkp > 64 * nt ? dkp : 64 * nt;  // the value columns a warp reads may lie beyond Dk
+  return widest + 8;
+}
+
+}  // namespace
+
+extern "C" int asb_latent_attention_mma_supported(int rank, int rot) {
+  return rank >= 1 && rank <= 512 && smem_bytes(padded_key_stride(rank, rot)) <= 220 * 1024;
+}
+
+extern "C" void asb_latent_attention_mma_tile_shape(int H, int* QT, int* GC) {
+  *GC = H < MR ? H : MR;
+  *QT = MR / *GC;
+}
+
+extern "C" int asb_latent_attention_mma(float* out, const float* q, const void* pages, const int* block_tables,
+                                        const int* req_q_start, const int* req_pos_start, float* part_m, float* part_l,
+                                        float* part_acc, int num_tokens, int R, int H, int rank, int rot, int bs,
+                                        int table_width, int PS, int NP, float scale, cudaStream_t stream) {
+  if (num_tokens == 0 || R == 0) return 0;
+  if (!asb_latent_attention_mma_supported(rank, rot)) return asb::fail("latent_attention_mma: latent %d + %d is not taken", rank, rot);
+  if (NP < 1 || PS < KT || PS % KT) return asb::fail("latent_attention_mma: partition size %d must be a positive multiple of %d", PS, KT);
+  if (NP > 1 && (!part_m || !part_l || !part_acc)) return asb::fail("latent_attention_mma: %d partitions need scratch", NP);
+  if (NP > 65535) return asb::fail("latent_attention_mma: %d partitions exceed the grid", NP);
+  LatentParams p;
+  p.q = q; p.out = out; p.pages = (const __nv_bfloat16*)pages; p.block_tables = block_tables;
+  p.req_q_start = req_q_start; p.req_pos_start = req_pos_start; p.part_m = part_m; p.part_l = part_l; p.part_acc = part_acc;
+  p.R = R; p.H = H; p.rank = rank; p.Dk = rank + rot; p.DKP = (p.Dk + 15) / 16 * 16; p.LDK = padded_key_stride(rank, rot);
+  p.bs = bs; p.table_width = table_width;
+  asb_latent_attention_mma_tile_shape(H, &p.QT, &p.GC);
+  p.HC = (H + p.GC - 1) / p.GC;
+  p.PS = PS; p.NP = NP; p.scale = scale;
+  const size_t smem = smem_bytes(p.LDK);
+  if (rank <= 64) return launch_attention<1>(p, num_tokens, smem, stream);
+  if (rank <= 128) return launch_attention<2>(p, num_tokens, smem, stream);
+  if (rank <= 256) return launch_attention<4>(p, num_tokens, smem, stream);
+  return launch_attention<8>(p, num_tokens, smem, stream);
+}

@@ -4,9 +4,21 @@ sum back per token."""
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from atomserve_b200.ops.library import KernelLibraryError, check, dtype_code, lib, ptr, require_cuda, stream
+
+
+# Which kernels multiply the experts in bfloat16: "mma" (tensor cores, csrc/moe_mma.cu; the default
+# where K is a multiple of 8) or "simt" (the CUDA-core kernels that float32 always runs).
+EXPERT_KERNELS = os.environ.get("ATOMSERVE_B200_EXPERTS", "mma")
+
+
+def _tensor_cores(x: torch.Tensor, *weights: torch.Tensor) -> bool:
+    return (EXPERT_KERNELS == "mma" and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and all(t.data_ptr() % 16 == 0 for t in (x, *weights)))  # fmt: skip
 
 
 def route(z: torch.Tensor, *, experts: int, top: int, groups: int = 1, group_top: int = 2, keep: int = 1,
@@ -48,6 +60,10 @@ def experts_glu(x: torch.Tensor, row_token: torch.Tensor, offsets: torch.Tensor,
         raise KernelLibraryError("experts_glu: x [T, K] against gate and up [E, F, K] of one dtype, contiguous")
     pairs = row_token.shape[0]
     hidden = torch.empty(pairs, F, device=x.device, dtype=x.dtype)
+    if _tensor_cores(x, gate, up):
+        check(lib().asb_moe_glu_mma(ptr(hidden), ptr(x), ptr(row_token), ptr(offsets), ptr(gate), ptr(up), pairs, E, F, K,
+                                    float(limit), float(slope), float(shift), stream()))  # fmt: skip
+        return hidden
     check(lib().asb_moe_glu(ptr(hidden), ptr(x), ptr(row_token), ptr(offsets), ptr(gate), ptr(up), pairs, E, F, K,
                             float(limit), float(slope), float(shift), dtype_code(x), stream()))  # fmt: skip
     return hidden
@@ -60,6 +76,9 @@ def experts_down(hidden: torch.Tensor, offsets: torch.Tensor, down: torch.Tensor
     if hidden.shape[1] != F or hidden.dtype != down.dtype or not (hidden.is_contiguous() and down.is_contiguous()):
         raise KernelLibraryError("experts_down: hidden [pairs, F] against down [E, N, F] of one dtype, contiguous")
     y = torch.empty(hidden.shape[0], N, device=hidden.device, dtype=torch.float32)
+    if _tensor_cores(hidden, down):
+        check(lib().asb_moe_down_mma(ptr(y), ptr(hidden), ptr(offsets), ptr(down), hidden.shape[0], E, N, F, stream()))
+        return y
     check(lib().asb_moe_down(ptr(y), ptr(hidden), ptr(offsets), ptr(down), hidden.shape[0], E, N, F, dtype_code(hidden), stream()))
     return y
 

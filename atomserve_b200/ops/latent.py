@@ -4,11 +4,17 @@ write with the queries' rotation, the per-head products, and the attention."""
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
 from atomserve_b200.ops.attention import TARGET_BLOCKS
 from atomserve_b200.ops.library import FLOAT32, KernelLibraryError, check, dtype_code, lib, ptr, require_cuda, stream
+
+
+# Which kernel serves bfloat16 pages: "mma" (tensor cores, csrc/latent_attention_mma.cu; the default
+# where its sizes hold) or "simt" (the CUDA-core kernel that float32 always runs).
+ATTENTION_KERNEL = os.environ.get("ATOMSERVE_B200_LATENT_ATTENTION", "mma")
 
 
 def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int | None, q_lat: torch.Tensor, pages: torch.Tensor | None,
@@ -96,10 +102,16 @@ def latent_attention(q_lat: torch.Tensor, pages: torch.Tensor, block_tables: tor
         part_m = torch.empty(T * H * np_, device=out.device, dtype=torch.float32)
         part_l = torch.empty_like(part_m)
         part_acc = torch.empty(T * H * np_ * rank, device=out.device, dtype=torch.float32)
-    check(lib().asb_latent_attention(ptr(out), ptr(q_lat), ptr(pages), ptr(block_tables), ptr(req_q_start),
-                                     ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), T, num_requests, H, rank,
-                                     Dk - rank, pages.shape[2], block_tables.shape[1], ps, np_, float(scale),
-                                     dtype_code(pages), stream()))  # fmt: skip
+    if ATTENTION_KERNEL == "mma" and pages.dtype == torch.bfloat16 and lib().asb_latent_attention_mma_supported(rank, Dk - rank):
+        check(lib().asb_latent_attention_mma(ptr(out), ptr(q_lat), ptr(pages), ptr(block_tables), ptr(req_q_start),
+                                             ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), T, num_requests, H,
+                                             rank, Dk - rank, pages.shape[2], block_tables.shape[1], ps, np_, float(scale),
+                                             stream()))  # fmt: skip
+    else:
+        check(lib().asb_latent_attention(ptr(out), ptr(q_lat), ptr(pages), ptr(block_tables), ptr(req_q_start),
+                                         ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), T, num_requests, H, rank,
+                                         Dk - rank, pages.shape[2], block_tables.shape[1], ps, np_, float(scale),
+                                         dtype_code(pages), stream()))  # fmt: skip
     if np_ > 1:
         check(lib().asb_attention_reduce(ptr(out), ptr(part_m), ptr(part_l), ptr(part_acc), T * H, np_, rank, FLOAT32, stream()))
     return out

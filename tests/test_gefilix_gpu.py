@@ -308,9 +308,9 @@ def test_whole_then_token_by_token_then_portions(models, name, dtype):
 def test_mixed_requests_reusing_pages_and_slots(models, name, dtype):
     """Up to four live requests in four state slots, portions beside single tokens, in a pool so
     small that pages and slots freed by finished requests are taken again; every request appears
-    three times, each equal to itself alone."""
+    four times, each equal to itself alone."""
     cfg, bs, folder, ps, refs = models[name, dtype]
-    ps3, refs3 = ps * 3, refs * 3
+    ps3, refs3 = ps * 4, refs * 4
     biggest = sorted((-(-len(p) // 64) * 64 for p in ps3), reverse=True)
     rp = replayer(folder, dtype, bs, sum(biggest[:4]), max_live=4)
     rng = np.random.default_rng(11)
