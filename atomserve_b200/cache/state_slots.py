@@ -2,9 +2,9 @@
 
 Every running request holds one slot id in [0, num_slots) from admission until it finishes or
 is preempted. Parts that keep constant-size state per request (a recurrent mixer's state, a
-sampler's counters) register a buffer `[num_slots, *shape]` here and index it by slot; a
+sampler's counters) register a buffer `[num_slots + 1, *shape]` here and index it by slot; a
 slot's rows are zeroed when the slot is handed out, so no request sees its predecessor's
-state. Qwen3's attention keeps nothing here; the slot is taken all the same, so that adding
+state; each buffer has one extra row that belongs to no request (`pad_slot`). Qwen3's attention keeps nothing here; the slot is taken all the same, so that adding
 such a part changes no engine code. (The reference keeps per-request state only on the host:
 atomserve/sequence.py:60-83, atomserve/sampler.py:53-70.)
 """
@@ -25,8 +25,14 @@ class StateSlots:
     def register(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         if name in self.buffers:
             raise KeyError(f"state buffer {name!r} is already registered")
-        self.buffers[name] = torch.zeros((self.num_slots, *shape), dtype=dtype, device=self.device)
+        # one row more than there are slots: `pad_slot`, which the dummy requests that pad a
+        # captured decode step to its batch size read and write, so that no request's state is touched
+        self.buffers[name] = torch.zeros((self.num_slots + 1, *shape), dtype=dtype, device=self.device)
         return self.buffers[name]
+
+    @property
+    def pad_slot(self) -> int:
+        return self.num_slots
 
     @property
     def num_free(self) -> int:

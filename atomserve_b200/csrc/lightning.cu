@@ -14,6 +14,13 @@
 // tile of TT tokens is staged in shared memory at once and walked in registers. The tokens of a
 // request are walked in order whatever the step holds (a whole prompt, a portion, one decoded
 // token), so the result does not depend on how a prompt was cut.
+//
+// Long portions are cut into segments that run side by side (the caller names them by their row
+// bounds): each segment runs the recurrence from a zero state (mode 1) and leaves its own
+// contribution; asb_lightning_scan walks a request's segments in order, S <- decay^n S + own,
+// leaving the state each segment starts from and the request's final state in its slot; mode 2
+// then adds decay^(t - first + 1) S_first^T q_t to every token of a segment. The sums are the
+// recurrence's, grouped differently: equal beyond rounding.
 #include "common.cuh"
 
 namespace {
@@ -30,6 +37,8 @@ struct LightningParams {
   const float* decay;       // [H]
   int stride, q_off, k_off, v_off;
   int H, D, V, DS, act;
+  int zero_init;  // 1: the state starts at zero and is only written (a segment's local state)
+  int carry;      // 1: add each token's share of the state it started from instead of running the recurrence
 };
 
 __device__ __forceinline__ float silu(float z) { return z / (1.f + expf(-z)); }
@@ -58,9 +67,10 @@ lightning_kernel(const LightningParams p) {
 #pragma unroll
   for (int i = 0; i < RPT; ++i) {
     const int d = ds * RPT + i;
-    S[i] = (live && d < p.D) ? sp[(size_t)d * p.V] : 0.f;
+    S[i] = (live && d < p.D && !p.zero_init) ? sp[(size_t)d * p.V] : 0.f;
   }
   const T* proj = (const T*)p.proj;
+  float weight = 1.f;
   for (int t0 = row_lo; t0 < row_hi; t0 += kTokenTile) {
     const int nt = min(kTokenTile, row_hi - t0);
     __syncthreads();
@@ -86,6 +96,19 @@ lightning_kernel(const LightningParams p) {
       vs[i] = vv;
     }
     __syncthreads();
+    if (p.carry) {
+      // o_t += decay^(t - first + 1) * S_first^T q_t: what the tokens before this segment contribute
+      for (int t = 0; t < nt; ++t) {
+        const float* qr = qs + t * DP + ds * RPT;
+        float o = 0.f;
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) o = fmaf(S[i], qr[i], o);
+        for (int off = 1; off < DS; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+        weight *= dec;
+        if (ds == 0 && live) p.out[(size_t)(t0 + t) * p.H * p.V + h * p.V + col] += weight * o;
+      }
+      continue;
+    }
     for (int t = 0; t < nt; ++t) {
       const float vv = vs[t * CPB + cl];
       const float* kr = ks + t * DP + ds * RPT;
@@ -100,6 +123,7 @@ lightning_kernel(const LightningParams p) {
       if (ds == 0 && live) p.out[(size_t)(t0 + t) * p.H * p.V + h * p.V + col] = o;
     }
   }
+  if (p.carry) return;
 #pragma unroll
   for (int i = 0; i < RPT; ++i) {
     const int d = ds * RPT + i;
@@ -119,11 +143,45 @@ int launch(const LightningParams& p, int R, cudaStream_t stream) {
   return asb::check_launch("lightning_attention");
 }
 
+// Between the segments of a request: the state each segment starts from, and the request's state
+// after its last one. local[c] holds segment c's own contribution on entry and the state the
+// segment starts from on exit; an element per thread, the segments of a request in order.
+__global__ void lightning_scan_kernel(float* __restrict__ local, float* __restrict__ state,
+                                      const int* __restrict__ state_slots, const int* __restrict__ req_seg_start,
+                                      const int* __restrict__ seg_bounds, const float* __restrict__ decay, int H, int DV) {
+  asb::pdl_wait();
+  asb::pdl_launch_dependents();
+  const int r = blockIdx.x, h = blockIdx.y;
+  const float dec = decay[h], log_dec = logf(dec);
+  float* sp = state + ((size_t)state_slots[r] * H + h) * DV;
+  for (int e = blockIdx.z * blockDim.x + threadIdx.x; e < DV; e += gridDim.z * blockDim.x) {
+    float S = sp[e];
+    for (int c = req_seg_start[r]; c < req_seg_start[r + 1]; ++c) {
+      float* at = local + ((size_t)c * H + h) * DV + e;
+      const float own = *at;
+      *at = S;
+      const float n = (float)(seg_bounds[c + 1] - seg_bounds[c]);
+      S = fmaf(dec == 1.f ? 1.f : expf(n * log_dec), S, own);
+    }
+    sp[e] = S;
+  }
+}
+
 }  // namespace
+
+extern "C" int asb_lightning_scan(float* local, float* state, const int* state_slots, const int* req_seg_start,
+                                  const int* seg_bounds, const float* decay, int R, int H, int D, int V,
+                                  cudaStream_t stream) {
+  if (R == 0) return 0;
+  const int DV = D * V;
+  dim3 grid(R, H, (DV + 255) / 256 < 64 ? (DV + 255) / 256 : 64);
+  asb::launch(lightning_scan_kernel, grid, 256, 0, stream, local, state, state_slots, req_seg_start, seg_bounds, decay, H, DV);
+  return asb::check_launch("lightning_scan");
+}
 
 extern "C" int asb_lightning_attention(float* out, const void* proj, int stride, int q_off, int k_off, int v_off,
                                        float* state, const int* state_slots, const int* req_q_start,
-                                       const float* decay, int R, int H, int D, int V, int act, int dtype,
+                                       const float* decay, int R, int H, int D, int V, int act, int mode, int dtype,
                                        cudaStream_t stream) {
   if (R == 0) return 0;
   if (H < 1 || D < 1 || V < 1 || H > 65535) return asb::fail("lightning_attention: %d heads of %d x %d", H, D, V);
@@ -131,6 +189,8 @@ extern "C" int asb_lightning_attention(float* out, const void* proj, int stride,
   p.out = out; p.proj = proj; p.state = state; p.state_slots = state_slots; p.req_q_start = req_q_start;
   p.decay = decay; p.stride = stride; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off;
   p.H = H; p.D = D; p.V = V; p.act = act;
+  p.zero_init = mode == 1;  // mode 0: the recurrence from the slots' states; 1: from zero, per segment; 2: the carried share
+  p.carry = mode == 2;
   // rows of the state per thread: 64 from D = 64 on, fewer for narrow heads; D beyond 64 is
   // shared among 2, 4, ... lanes
   const int rpt = D >= 64 ? 64 : (D > 16 ? 32 : 16);

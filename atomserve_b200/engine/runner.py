@@ -128,9 +128,12 @@ class ModelRunner:
         # how kernels report that they could not finish (none on the CPU stand-ins of the tests)
         self.device_status = status_for(self.device) if self.device.type == "cuda" else None
         self.views: list[CacheView | None] = [cache.entry_view(i) for i in range(len(model.schedule))]
-        # Graphs replay the same kernels on new inputs; a part that updates state of its own in
-        # place would be run again by capture and warm-up, so such models step eagerly.
-        self.use_graphs = cuda_graphs and self.device.type == "cuda" and not cache.entry_state
+        # Graphs replay the same kernels on new inputs. A part that updates state of its own in
+        # place is run once more by the warm-up before a capture: where every such mixer says that
+        # its state may be saved and put back around that run (`state_in_graphs`), the runner does
+        # so; otherwise such models step eagerly.
+        state_ok = all(getattr(model.blocks[model.schedule[i].layer].mixer, "state_in_graphs", False) for i in cache.entry_state)
+        self.use_graphs = cuda_graphs and self.device.type == "cuda" and state_ok
         self._copy_done: torch.cuda.Event | None = None
         self._graphs = GraphCache()
         self._graph_pool = None
@@ -292,8 +295,9 @@ class ModelRunner:
                 b += 1
             flat += n
             max_context = max(max_context, r.start + n)
+        pad_slot = self.cache.state.pad_slot  # state that belongs to no request
         for i in range(real, R):  # padding requests
-            tok[flat], pos[flat], qs[i], ps[i], ss[i], lr[b] = 0, 0, flat, 0, 0, flat
+            tok[flat], pos[flat], qs[i], ps[i], ss[i], lr[b] = 0, 0, flat, 0, pad_slot, flat
             flat += 1
             b += 1
         qs[R] = flat
@@ -334,7 +338,7 @@ class ModelRunner:
             req_q_start=dv["req_q_start"], req_pos_start=dv["req_pos_start"],
             state_slots=dv["state_slots"], logits_rows=dv["logits_rows"], max_context=max_context,
             host_q_lens=[len(r.tokens) for r in rows] + [1] * pad, host_pos_start=[r.start for r in rows] + [0] * pad,
-            host_state_slots=[r.cache.state_slot for r in rows] + [0] * pad,
+            host_state_slots=[r.cache.state_slot for r in rows] + [pad_slot] * pad,
         )  # fmt: skip
         groups = [(dv[f"slots{g}"], dv[f"tables{g}"].view(R, w)) for g, w in enumerate(widths)]
         return ctx, groups, (T, R, tuple(widths), B)
@@ -394,8 +398,15 @@ class ModelRunner:
         logits = self._graph_logits[:out_rows]
         entry = self._graphs.get(key)
         if entry is None:
-            # warm up outside capture (lazy library initialisation must not be captured)
+            # warm up outside capture (lazy library initialisation must not be captured); the state
+            # that the run advances is put back, since the replay below is the step that counts
+            saved = []
+            if self.cache.entry_state:
+                held = torch.tensor(sorted({r.cache.state_slot for r in rows}), device=self.device)
+                saved = [(buf, buf[held].clone()) for buf in self.cache.state.buffers.values()]
             self.model.forward(ctx, self.views, logits)
+            for buf, before in saved:
+                buf[held] = before
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:

@@ -55,7 +55,8 @@ _SIGNATURES = {
     "asb_gelu": [_P, _P, ctypes.c_longlong, _I, _I, _P],
     "asb_clamped_glu": [_P, _P, _I, _I, _F, _F, _F, _I, _P],
     # linear attention with a decay per head
-    "asb_lightning_attention": [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "asb_lightning_attention": [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "asb_lightning_scan": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     # attention over a cached latent
     "asb_latent_prepare": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "asb_head_matmul": [_P, _I, _I, _I, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P],

@@ -18,6 +18,8 @@ from atomserve_b200.parts.spec import TensorSpec
 
 
 class LightningAttention(Mixer):
+    state_in_graphs = True  # the state is touched by this mixer's kernel alone, through ctx.state_slots
+
     def __init__(self, hidden_size: int, prefix: str, heads: int, dim: int, vdim: int, decay: list[float], eps: float,
                  activation: str = "silu"):  # fmt: skip
         if len(decay) != heads:
@@ -51,8 +53,13 @@ class LightningAttention(Mixer):
                 cache: CacheView | None, write_cache: bool = True) -> torch.Tensor:  # fmt: skip
         qk, vg = self.heads * self.dim, self.heads * self.vdim
         proj = ops.linear(h, self.in_proj)
+        # long portions are cut into segments that run side by side; the cut is made once per step
+        # and shared by the step's layers
+        if not hasattr(ctx, "lightning_segments"):
+            ctx.lightning_segments = ops.plan_segments(ctx.host_q_lens, h.device) if ctx.host_q_lens else None
         o = ops.lightning_attention(proj, 0, qk, 2 * qk, cache.state["s"], ctx.state_slots, ctx.req_q_start, self.decay,
-                                    ctx.num_requests, activation=self.activation == "silu")  # fmt: skip
+                                    ctx.num_requests, activation=self.activation == "silu",
+                                    segments=ctx.lightning_segments)  # fmt: skip
         gated = ops.gated_rms_norm(o, proj[:, 2 * qk + vg :], self.gain, self.eps)
         # without a residual (a block that sums in float32 itself) the product stays float32
         return ops.linear(gated, self.o_proj, residual, out_dtype=torch.float32 if residual is None else None)

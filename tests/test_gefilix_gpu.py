@@ -100,6 +100,41 @@ def test_lightning_attention_alone(dtype, H, D, V):
     assert out.dtype == torch.float32
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,D,V", [(3, 24, 40), (2, 96, 20), (2, 64, 64)])
+def test_lightning_attention_in_segments(dtype, H, D, V):
+    """Portions long enough to be cut into segments that run side by side: after a first portion
+    that leaves a state, beside short requests in the same step, and followed by single tokens;
+    segments of 64 tokens, the last one ragged; equal to the recurrence token by token."""
+    from atomserve_b200.parts import CacheView, PartSpec, build_part
+
+    d = 48
+    g = torch.Generator().manual_seed(H + D)
+    m = dict(heads=H, dim=D, vdim=V, decay=[0.97, 1.0, 0.5][:H])
+    shapes = {"q": (H * D, d), "k": (H * D, d), "v": (H * V, d), "g": (H * V, d), "o": (d, H * V)}
+    w = {"m." + n: rounded(torch.randn(s, generator=g) * s[1] ** -0.5) for n, s in shapes.items()}
+    w["m.norm"] = 1 + 0.1 * torch.randn(H * V, generator=g)
+    part = build_part("mixer", PartSpec("lightning_attention", dict(m, eps=EPS), "m."), d)
+    part.load(on_device(w, dtype))
+    lens = [20 + 300 + 3, 1, 5, 256]
+    hs = [rounded(torch.randn(n, d, generator=g)) for n in lens]
+    refs = [plain.lightning_mixer({k: v.double() for k, v in w.items()}, "m.", m, EPS, h.double())[0].float() for h in hs]
+    view = CacheView(state={"s": torch.zeros(5, H, D, V, device="cuda")})
+
+    def run(pieces, starts, slots):
+        h = torch.cat(pieces).cuda().to(dtype)
+        return part.forward(h, None, step_context([len(x) for x in pieces], starts, slots), view).float().cpu()
+
+    first = run([hs[0][:20]], [0], [3])
+    both = run([hs[0][20:320], hs[1], hs[2], hs[3]], [20, 0, 0, 0], [3, 0, 4, 1])
+    last = torch.cat([run([hs[0][320 + i : 321 + i]], [320 + i], [3]) for i in range(3)])
+    tol = 0.05
+    check(torch.cat([first, both[:300], last]), refs[0], dtype, "a long portion between a short one and single tokens", tol)
+    check(both[300:301], refs[1], dtype, "one token beside it", tol)
+    check(both[301:306], refs[2], dtype, "five tokens beside it", tol)
+    check(both[306:], refs[3], dtype, "a portion of exactly four segments", tol)
+
+
 def latent_weights(g, d, m, own):
     H, D, Rt, V, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     shapes = {"q": (H * (D + Rt), d), "uk": (H * D, R), "uv": (H * V, R), "g": (H, d), "o": (d, H * V)}
