@@ -4,7 +4,8 @@
 //
 // A block owns 32 (token, head) rows, the heads of one or a few neighbouring tokens of a
 // request, which all read the same keys: one shared key head of width Dk = rank + rot, whose
-// first `rank` entries are also the values. Per tile of 64 keys, staged once in shared memory:
+// first `rank` entries are also the values. Per tile of 64 keys, staged once in shared memory
+// (cp.async, the next tile arriving while this one is multiplied):
 //   1. each of the 8 warps multiplies the 32 query rows with 8 of the keys (k over Dk) and
 //      writes the scaled, masked float32 scores to shared memory;
 //   2. each warp runs the online softmax of 4 of the rows: running maximum and sum in float32,
@@ -53,6 +54,17 @@ __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t (&b)[2], const void* 
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b[0]), "=r"(b[1]) : "r"(addr));
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* row) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], const void* row) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+
 // NT: 8-column tiles of the output per warp; the block covers 64 * NT >= rank columns
 template <int NT>
 __global__ void __launch_bounds__(kWarps * 32)
@@ -62,8 +74,8 @@ latent_attention_mma_kernel(const LatentParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int Dk = p.Dk, Dv = p.rank, DKP = p.DKP, LDK = p.LDK;
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [MR][LDK]
-  __nv_bfloat16* k_s = q_s + MR * LDK;                               // [KT][LDK] (+ slack the launcher adds)
-  __nv_bfloat16* p_s = k_s + (KT + 1) * LDK;                         // [MR][LDP]
+  __nv_bfloat16* k_buf = q_s + MR * LDK;                             // 2 x [KT][LDK]: one tile multiplied, the next one arriving
+  __nv_bfloat16* p_s = k_buf + 2 * KT * LDK;                         // [MR][LDP]
   float* s_s = reinterpret_cast<float*>(p_s + MR * LDP);             // [MR][LDS]
   float* row_m = s_s + MR * LDS;                                     // [MR]
   float* row_l = row_m + MR;
@@ -91,18 +103,34 @@ latent_attention_mma_kernel(const LatentParams p) {
   const int key_lo = blockIdx.z * p.PS;
   const int key_hi = (int)min((long long)hi, (long long)(blockIdx.z + 1) * p.PS);
 
-  // queries as bfloat16, rows beyond the block's and columns beyond Dk zero
-  for (int i = threadIdx.x; i < MR * LDK; i += blockDim.x) {
-    const int rr = i / LDK, e = i - rr * LDK;
-    float v = 0.f;
-    if (rr < num_rows && e < Dk) {
+  // queries as bfloat16, a warp per row, rows beyond the block's and columns beyond Dk zero
+  const bool q4 = (Dk % 4 == 0) && (((uintptr_t)p.q & 15) == 0);
+  for (int rr = warp; rr < MR; rr += kWarps) {
+    __nv_bfloat16* dst = q_s + rr * LDK;
+    const float* src = nullptr;
+    if (rr < num_rows) {
       const int qi = rr / gc, gg = rr - qi * gc;
-      v = p.q[((size_t)(row0 + qi) * p.H + head0 + gg) * Dk + e];
+      src = p.q + ((size_t)(row0 + qi) * p.H + head0 + gg) * Dk;
     }
-    q_s[i] = __float2bfloat16_rn(v);
+    if (src && q4) {
+      for (int e = lane * 4; e < Dk; e += 128) {
+        const float4 v = *reinterpret_cast<const float4*>(src + e);
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(dst + e) = packed;
+      }
+      for (int e = Dk + lane; e < LDK; e += 32) dst[e] = __float2bfloat16_rn(0.f);
+    } else {
+      for (int e = lane; e < LDK; e += 32) dst[e] = __float2bfloat16_rn((src && e < Dk) ? src[e] : 0.f);
+    }
   }
-  // the key tile's columns beyond Dk, and the slack behind it, stay zero
-  for (int i = threadIdx.x; i < (KT + 1) * LDK; i += blockDim.x) k_s[i] = __float2bfloat16_rn(0.f);
+  // the key tiles' columns beyond Dk stay zero (every tile rewrites the Dk columns of all its rows)
+  for (int i = threadIdx.x; i < 2 * KT * (LDK - Dk); i += blockDim.x) {
+    const int jj = i / (LDK - Dk), e = Dk + i - jj * (LDK - Dk);
+    k_buf[jj * LDK + e] = __float2bfloat16_rn(0.f);
+  }
   if (threadIdx.x < MR) {
     row_m[threadIdx.x] = -INFINITY;
     row_l[threadIdx.x] = 0.f;
@@ -119,22 +147,36 @@ latent_attention_mma_kernel(const LatentParams p) {
   const bool vector = (Dk % 8 == 0) && (((uintptr_t)p.pages & 15) == 0);
   const int chunks = Dk / 8;
 
-  for (int kt0 = (key_lo / KT) * KT; kt0 < key_hi; kt0 += KT) {
-    __syncthreads();  // the previous tile's keys and weights have been read
+  // A tile's keys: 16-byte asynchronous copies where the rows allow them (Dk a multiple of 8),
+  // keys outside the block's range filled with zeros; the tile after the one being multiplied is
+  // always on its way. Other widths are copied element by element when their turn comes.
+  auto request_tile = [&](int kt0, __nv_bfloat16* k_s) {
+    for (int i = threadIdx.x; i < KT * chunks; i += blockDim.x) {
+      const int jj = i / chunks, c = i - jj * chunks;
+      const int j = kt0 + jj;
+      const bool in = j >= key_lo && j < key_hi;
+      const __nv_bfloat16* src = in ? p.pages + ((size_t)table[j / p.bs] * p.bs + j % p.bs) * Dk + c * 8 : p.pages;
+      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(k_s + jj * LDK + c * 8);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(in ? 16 : 0) : "memory");
+    }
+  };
+  const int first_tile = (key_lo / KT) * KT;
+  __syncthreads();  // the zeros are in place before any copy lands on them
+  if (vector && first_tile < key_hi) request_tile(first_tile, k_buf);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+
+  for (int kt0 = first_tile, turn = 0; kt0 < key_hi; kt0 += KT, turn ^= 1) {
+    __nv_bfloat16* k_s = k_buf + turn * KT * LDK;
     if (threadIdx.x < KT) {
       const int j = kt0 + threadIdx.x;
       block_of_key[threadIdx.x] = (j >= key_lo && j < key_hi) ? table[j / p.bs] : -1;
     }
-    __syncthreads();
     if (vector) {
-      for (int i = threadIdx.x; i < KT * chunks; i += blockDim.x) {
-        const int jj = i / chunks, c = i - jj * chunks;
-        const int blk = block_of_key[jj];
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (blk >= 0) v = *reinterpret_cast<const uint4*>(p.pages + ((size_t)blk * p.bs + (kt0 + jj) % p.bs) * Dk + c * 8);
-        *reinterpret_cast<uint4*>(k_s + jj * LDK + c * 8) = v;
-      }
+      if (kt0 + KT < key_hi) request_tile(kt0 + KT, k_buf + (turn ^ 1) * KT * LDK);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 1;" ::: "memory");  // all but the newest group: this tile has arrived
     } else {
+      __syncthreads();
       for (int i = threadIdx.x; i < KT * Dk; i += blockDim.x) {
         const int jj = i / Dk, e = i - jj * Dk;
         const int blk = block_of_key[jj];
@@ -146,21 +188,38 @@ latent_attention_mma_kernel(const LatentParams p) {
     // 1. scores of the 32 rows against this warp's 8 keys
     {
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      const __nv_bfloat16* kb = k_s + (warp * 8 + g) * LDK;
-      for (int kk = 0; kk < DKP; kk += 16) {
-        uint32_t b[2];
-        b[0] = *reinterpret_cast<const uint32_t*>(kb + kk + 2 * t);
-        b[1] = *reinterpret_cast<const uint32_t*>(kb + kk + 2 * t + 8);
+      // fragments by ldmatrix: a lane names one row of one 8 x 8 block. Queries: rows (lane % 16) of
+      // each 16-row tile, k block lane / 16; keys: this warp's 8 keys, k block (lane / 8) % 2 (x2) or
+      // lane / 8 (x4, two k steps at once)
+      const __nv_bfloat16* qa0 = q_s + (lane & 15) * LDK + (lane >> 4) * 8;
+      const __nv_bfloat16* qa1 = qa0 + 16 * LDK;
+      const __nv_bfloat16* kb = k_s + (warp * 8 + (lane & 7)) * LDK + (lane >> 3) * 8;
+      int kk = 0;
+      float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};  // odd k steps: four chains of dependent MMAs, not two
+      for (; kk + 32 <= DKP; kk += 32) {
+        uint32_t b4[4], a0[4], a1[4], a2[4], a3[4];
+        ldmatrix_x4(b4, kb + kk);
+        ldmatrix_x4(a0, qa0 + kk);
+        ldmatrix_x4(a1, qa1 + kk);
+        ldmatrix_x4(a2, qa0 + kk + 16);
+        ldmatrix_x4(a3, qa1 + kk + 16);
+        const uint32_t b_lo[2] = {b4[0], b4[1]}, b_hi[2] = {b4[2], b4[3]};
+        mma_bf16(s[0], a0, b_lo);
+        mma_bf16(s[1], a1, b_lo);
+        mma_bf16(s2[0], a2, b_hi);
+        mma_bf16(s2[1], a3, b_hi);
+      }
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const __nv_bfloat16* qa = q_s + (i * 16 + g) * LDK + kk + 2 * t;
-          uint32_t a[4];
-          a[0] = *reinterpret_cast<const uint32_t*>(qa);
-          a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * LDK);
-          a[2] = *reinterpret_cast<const uint32_t*>(qa + 8);
-          a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * LDK + 8);
-          mma_bf16(s[i], a, b);
-        }
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s[i][c] += s2[i][c];
+      if (kk < DKP) {
+        uint32_t b[2], a[4];
+        ldmatrix_x2(b, k_s + (warp * 8 + (lane & 7)) * LDK + ((lane >> 3) & 1) * 8 + kk);
+        ldmatrix_x4(a, qa0 + kk);
+        mma_bf16(s[0], a, b);
+        ldmatrix_x4(a, qa1 + kk);
+        mma_bf16(s[1], a, b);
       }
 #pragma unroll
       for (int i = 0; i < 2; ++i)
@@ -233,8 +292,8 @@ latent_attention_mma_kernel(const LatentParams p) {
         }
       }
     }
+    __syncthreads();  // this tile's keys, weights and key table have been read
   }
-  __syncthreads();
 
 #pragma unroll
   for (int i = 0; i < 2; ++i)
@@ -262,6 +321,118 @@ latent_attention_mma_kernel(const LatentParams p) {
     }
 }
 
+// ---- per-head products on the tensor cores ------------------------------------------------------
+//
+// out[t, h, :] = x[t, h, :] . w[h]^T for w [H, N, K] (bfloat16, K contiguous), optionally times
+// sigmoid(gate[t, h]): the query absorption (x bfloat16, out float32) and the value up-projection
+// with the output gate (x float32, rounded to bfloat16 on the way in; out bfloat16). A block
+// computes 64 tokens x 64 columns of one head, four warps of 32 x 32, K in steps of 32.
+
+constexpr int HB = 64, HK = 32, HLD = HK + 8;
+
+template <typename TX, typename TO>
+__global__ void __launch_bounds__(128)
+head_matmul_mma_kernel(TO* __restrict__ out, int out_row, int out_head, const TX* __restrict__ x, int x_row, int x_head,
+                       const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ gate, int gate_row,
+                       int T, int K, int N) {
+  asb::pdl_wait();
+  asb::pdl_launch_dependents();
+  __shared__ __align__(16) __nv_bfloat16 xs[HB][HLD];
+  __shared__ __align__(16) __nv_bfloat16 ws[HB][HLD];
+  const int t0 = blockIdx.x * HB, h = blockIdx.y, n0 = blockIdx.z * HB;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+  const __nv_bfloat16* wh = w + (size_t)h * N * K;
+  const int lrow0 = tid >> 2, lrow1 = lrow0 + 32, lchunk = (tid & 3) * 8;
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += HK) {
+    __syncthreads();
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int lr = half ? lrow1 : lrow0;
+      const int tok = t0 + lr, n = n0 + lr, k = k0 + lchunk;
+      uint4 wv = make_uint4(0, 0, 0, 0);
+      if (n < N && k < K) wv = *reinterpret_cast<const uint4*>(wh + (size_t)n * K + k);
+      *reinterpret_cast<uint4*>(&ws[lr][lchunk]) = wv;
+      const TX* xp = x + (size_t)tok * x_row + (size_t)h * x_head + k;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) xs[lr][lchunk + u] = (tok < T && k + u < K) ? __float2bfloat16_rn(asb::to_float(xp[u])) : __float2bfloat16_rn(0.f);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < HK; kk += 16) {
+      uint32_t a[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int r = wm + i * 16 + g;
+        a[i][0] = *reinterpret_cast<const uint32_t*>(&xs[r][kk + 2 * t]);
+        a[i][1] = *reinterpret_cast<const uint32_t*>(&xs[r + 8][kk + 2 * t]);
+        a[i][2] = *reinterpret_cast<const uint32_t*>(&xs[r][kk + 2 * t + 8]);
+        a[i][3] = *reinterpret_cast<const uint32_t*>(&xs[r + 8][kk + 2 * t + 8]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = wn + j * 8 + g;
+        uint32_t b[2];
+        b[0] = *reinterpret_cast<const uint32_t*>(&ws[n][kk + 2 * t]);
+        b[1] = *reinterpret_cast<const uint32_t*>(&ws[n][kk + 2 * t + 8]);
+        mma_bf16(acc[0][j], a[0], b);
+        mma_bf16(acc[1][j], a[1], b);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int tok = t0 + wm + i * 16 + g + half * 8;
+      if (tok >= T) continue;
+      float scale = 1.f;
+      if (gate) scale = 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)tok * gate_row + h])));
+      TO* orow = out + (size_t)tok * out_row + (size_t)h * out_head;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int n = n0 + wn + j * 8 + 2 * t + c;
+          if (n < N) orow[n] = asb::from_float<TO>(acc[i][j][half * 2 + c] * scale);
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" int asb_head_matmul_mma_supported(int K) { return K >= 8 && K % 8 == 0; }
+
+// w: [H, N, K] bfloat16. x: float32 (x_f32 1) or bfloat16; out: float32 (out_f32 1) or bfloat16.
+extern "C" int asb_head_matmul_mma(void* out, int out_f32, int out_row, int out_head, const void* x, int x_f32, int x_row,
+                                   int x_head, const void* w, const void* gate, int gate_row, int T, int H, int K, int N,
+                                   cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (!asb_head_matmul_mma_supported(K) || ((uintptr_t)w & 15)) return asb::fail("head_matmul_mma: K = %d must be a multiple of 8 and w 16-byte aligned", K);
+  if (H > 65535 || (N + HB - 1) / HB > 65535) return asb::fail("head_matmul_mma: %d heads of %d columns exceed the grid", H, N);
+  dim3 grid((T + HB - 1) / HB, H, (N + HB - 1) / HB);
+  using B = __nv_bfloat16;
+  if (x_f32 && out_f32)
+    asb::launch(head_matmul_mma_kernel<float, float>, grid, 128, 0, stream, (float*)out, out_row, out_head, (const float*)x, x_row, x_head, (const B*)w, (const B*)gate, gate_row, T, K, N);
+  else if (x_f32)
+    asb::launch(head_matmul_mma_kernel<float, B>, grid, 128, 0, stream, (B*)out, out_row, out_head, (const float*)x, x_row, x_head, (const B*)w, (const B*)gate, gate_row, T, K, N);
+  else if (out_f32)
+    asb::launch(head_matmul_mma_kernel<B, float>, grid, 128, 0, stream, (float*)out, out_row, out_head, (const B*)x, x_row, x_head, (const B*)w, (const B*)gate, gate_row, T, K, N);
+  else
+    asb::launch(head_matmul_mma_kernel<B, B>, grid, 128, 0, stream, (B*)out, out_row, out_head, (const B*)x, x_row, x_head, (const B*)w, (const B*)gate, gate_row, T, K, N);
+  return asb::check_launch("head_matmul_mma");
+}
+
+namespace {
+
 template <int NT>
 int launch_attention(const LatentParams& p, int num_tokens, size_t smem, cudaStream_t stream) {
   auto kern = latent_attention_mma_kernel<NT>;
@@ -273,7 +444,7 @@ int launch_attention(const LatentParams& p, int num_tokens, size_t smem, cudaStr
 }
 
 size_t smem_bytes(int LDK) {
-  return sizeof(__nv_bfloat16) * ((size_t)(MR + KT + 1) * LDK + MR * LDP) + sizeof(float) * (MR * LDS + 3 * MR);
+  return sizeof(__nv_bfloat16) * ((size_t)(MR + 2 * KT) * LDK + MR * LDP) + sizeof(float) * (MR * LDS + 3 * MR);
 }
 
 int padded_key_stride(int rank, int rot) {

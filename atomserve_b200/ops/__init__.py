@@ -14,7 +14,7 @@ from atomserve_b200.ops.elementwise import (
     silu_mul,
 )
 from atomserve_b200.ops.experts import combine, experts_down, experts_glu, group_by_expert, route
-from atomserve_b200.ops.latent import head_matmul, latent_attention, latent_prepare
+from atomserve_b200.ops.latent import head_matmul, head_matmul_on_tensor_cores, latent_attention, latent_prepare
 from atomserve_b200.ops.library import KernelLibraryError, require_device
 from atomserve_b200.ops.recurrent import lightning_attention, plan_segments
 from atomserve_b200.ops.linear import PartialSums, interleave_gate_up, linear, linear_partial, linear_swiglu, swiglu_fusable
@@ -24,7 +24,7 @@ from atomserve_b200.ops.stream import cast_rows, clamped_glu, embedding_scaled, 
 
 __all__ = [
     "cast_rows", "clamped_glu", "combine", "embedding_scaled", "experts_down", "experts_glu", "gated_rms_norm", "gelu",
-    "group_by_expert", "head_matmul", "latent_attention", "latent_prepare", "lightning_attention", "plan_segments", "route",
+    "group_by_expert", "head_matmul", "head_matmul_on_tensor_cores", "latent_attention", "latent_prepare", "lightning_attention", "plan_segments", "route",
     "scaled_add_rms_norm",
     "DeviceStatus",
     "KernelLibraryError",

@@ -44,12 +44,20 @@ def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int | None, q_lat: to
                                    float(eps), dtype_code(proj), stream()))  # fmt: skip
 
 
-def head_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: torch.Tensor | None = None) -> torch.Tensor:
-    """out[t, h, :] = x[t, h, :] . w[h] for w [H, K, N] in the compute dtype, times
-    sigmoid(gate[t, h]) where a gate is given. x [T, H, K] and out [T, H, N] are float32 or the
-    compute dtype and may be strided views with unit stride along the last axis."""
+def head_matmul_on_tensor_cores(w: torch.Tensor, k: int) -> bool:
+    """Whether per-head products with this weight dtype and inner size run the tensor-core kernel,
+    which takes the weights as [H, N, K]."""
+    return ATTENTION_KERNEL == "mma" and w.dtype == torch.bfloat16 and k % 8 == 0
+
+
+def head_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: torch.Tensor | None = None,
+                w_is_nk: bool = False) -> torch.Tensor:  # fmt: skip
+    """out[t, h, :] = x[t, h, :] . w[h], times sigmoid(gate[t, h]) where a gate is given. w is
+    [H, K, N] in the compute dtype, or with `w_is_nk` [H, N, K] in bfloat16 (the tensor-core
+    kernel's layout). x [T, H, K] and out [T, H, N] are float32 or the compute dtype and may be
+    strided views with unit stride along the last axis."""
     require_cuda(x, w, out, gate)
-    H, K, N = w.shape
+    H, K, N = (w.shape[0], w.shape[2], w.shape[1]) if w_is_nk else w.shape
     T = x.shape[0]
     if x.shape != (T, H, K) or out.shape != (T, H, N) or x.stride(2) != 1 or out.stride(2) != 1 or not w.is_contiguous():
         raise KernelLibraryError(f"head_matmul: x {tuple(x.shape)} . w {tuple(w.shape)} -> out {tuple(out.shape)}")
@@ -58,6 +66,13 @@ def head_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: torch
             raise KernelLibraryError("head_matmul: x and out are float32 or w's dtype")
     if gate is not None and (gate.shape != (T, H) or gate.dtype != w.dtype or gate.stride(1) != 1):
         raise KernelLibraryError("head_matmul: gate must be [T, H] in w's dtype with unit column stride")
+    if w_is_nk:
+        if not head_matmul_on_tensor_cores(w, K) or w.data_ptr() % 16:
+            raise KernelLibraryError("head_matmul: [H, N, K] weights are bfloat16 with K a multiple of 8")
+        check(lib().asb_head_matmul_mma(ptr(out), int(out.dtype == torch.float32), out.stride(0), out.stride(1), ptr(x),
+                                        int(x.dtype == torch.float32), x.stride(0), x.stride(1), ptr(w), ptr(gate),
+                                        gate.stride(0) if gate is not None else 0, T, H, K, N, stream()))  # fmt: skip
+        return out
     check(lib().asb_head_matmul(ptr(out), int(out.dtype == torch.float32), out.stride(0), out.stride(1), ptr(x),
                                 int(x.dtype == torch.float32), x.stride(0), x.stride(1), ptr(w), ptr(gate),
                                 gate.stride(0) if gate is not None else 0, T, H, K, N, dtype_code(w), stream()))  # fmt: skip

@@ -63,6 +63,7 @@ _SIGNATURES = {
     "asb_latent_attention": [_P] * 9 + [_I] * 9 + [_F, _I, _P],
     "asb_latent_attention_mma": [_P] * 9 + [_I] * 9 + [_F, _P],
     "asb_latent_attention_mma_supported": [_I, _I],
+    "asb_head_matmul_mma": [_P, _I, _I, _I, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _P],
     # routed experts
     "asb_moe_route": [_P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _P],
     "asb_moe_group": [_P, _I, _I, _I, _P, _P, _P, _P],

@@ -59,8 +59,13 @@ class LatentAttention(Mixer):
         # queries, (down-projection,) gates stacked along the output rows: one product
         rows = [tensors[p + "q"]] + ([] if self.reads_only else [tensors[p + "dkv"]]) + [tensors[p + "g"]]
         self.in_proj = torch.cat(rows).contiguous()
-        self.uk = tensors[p + "uk"].view(H, self.dim, self.kv_rank).contiguous()  # [h][dim][rank]: absorbs into q
-        self.uv_t = tensors[p + "uv"].view(H, self.vdim, self.kv_rank).transpose(1, 2).contiguous()  # [h][rank][vdim]
+        # per head, keys' up-projection [dim, rank] (absorbed into the queries) and values' [rank, vdim];
+        # the tensor-core kernel takes each with its inner size last instead
+        uk, uv = tensors[p + "uk"].view(H, self.dim, self.kv_rank), tensors[p + "uv"].view(H, self.vdim, self.kv_rank)
+        self.uk_nk = ops.head_matmul_on_tensor_cores(uk, self.dim)
+        self.uv_nk = ops.head_matmul_on_tensor_cores(uv, self.kv_rank)
+        self.uk = (uk.transpose(1, 2) if self.uk_nk else uk).contiguous()
+        self.uv_t = (uv if self.uv_nk else uv.transpose(1, 2)).contiguous()
         self.o_proj = tensors[p + "o"]
         self.latent_gain = None if self.reads_only else tensors[p + "dkv.norm"]
         self.position.prepare(self.o_proj.device)
@@ -79,14 +84,14 @@ class LatentAttention(Mixer):
         proj = ops.linear(h, self.in_proj)
         pages = cache.pages[PAGE]
         q_lat = torch.empty(T, H, R + Rt, device=h.device, dtype=torch.float32)
-        ops.head_matmul(proj[:, :q_cols].view(T, H, D + Rt)[:, :, :D], self.uk, q_lat[:, :, :R])
+        ops.head_matmul(proj[:, :q_cols].view(T, H, D + Rt)[:, :, :D], self.uk, q_lat[:, :, :R], w_is_nk=self.uk_nk)
         ops.latent_prepare(proj, 0, None if self.reads_only else q_cols, q_lat, None if self.reads_only else pages,
                            self.latent_gain, self.rotary.inv_freq, ctx.positions, None if self.reads_only else cache.slots,
                            heads=H, dim=D, rank=R, rot=Rt, rot_dims=self.rotary.rotary_dim, eps=self.eps)  # fmt: skip
         mixed = ops.latent_attention(q_lat, pages, cache.block_tables, ctx.req_q_start, ctx.req_pos_start, rank=R,
                                      num_requests=ctx.num_requests, max_context=ctx.max_context, scale=self.scale)  # fmt: skip
         out = torch.empty(T, H * V, device=h.device, dtype=h.dtype)
-        ops.head_matmul(mixed, self.uv_t, out.view(T, H, V), gate=proj[:, gate_off : gate_off + H])
+        ops.head_matmul(mixed, self.uv_t, out.view(T, H, V), gate=proj[:, gate_off : gate_off + H], w_is_nk=self.uv_nk)
         # without a residual (a block that sums in float32 itself) the product stays float32
         return ops.linear(out, self.o_proj, residual, out_dtype=torch.float32 if residual is None else None)
 

@@ -602,7 +602,8 @@ def time_designs(widths: list[int], layers: int, steps: int, warmup: int, pk: di
         proj = torch.randn(T, 4 * H * D, device="cuda", dtype=bf)
         state = torch.zeros(B, H, D, D, device="cuda")
         decay = torch.full((H,), 0.99, device="cuda")
-        ms = timed(lambda: ops.lightning_attention(proj, 0, H * D, 2 * H * D, state, i32([0]), i32([0, T]), decay, 1))
+        segments = ops.plan_segments([T], proj.device)
+        ms = timed(lambda: ops.lightning_attention(proj, 0, H * D, 2 * H * D, state, i32([0]), i32([0, T]), decay, 1, segments=segments))
         kern["lightning_prefill"] = {"ms": round(ms, 4), "gflops": round(4.0 * T * H * D * D / ms / 1e6, 1), "note": "float32 CUDA cores"}
         ms = timed(lambda: ops.lightning_attention(proj[:B], 0, H * D, 2 * H * D, state, i32(list(range(B))), i32(list(range(B + 1))), decay, B))
         kern["lightning_decode_b64"] = {"ms": round(ms, 4), "hbm_frac": round(2.0 * B * H * D * D * 4 / (ms * 1e-3) / bw, 3)}

@@ -262,7 +262,7 @@ def test_feed_forwards_alone(dtype):
     assert out.dtype == torch.float32
     check(out, plain.dense_feed_forward({k: v.double() for k, v in w.items()}, "f.", h.double()).float(), dtype, "dense", 0.02)
     # routed experts of three kinds; equal inputs, so selection is the oracle's in bfloat16 too
-    for E, top, groups, ff_size, limit, shared in ((6, 2, (3, 2), 48, 1.5, (32, 3.0)), (4, 1, None, 40, 0.5, None),
+    for E, top, groups, ff_size, limit, shared in ((6, 2, (3, 2), 48, 1.5, (32, 3.0)), (4, 1, None, 36, 0.5, None),
                                                    (16, 4, (2, 1), 72, 2.0, (24, 1.0))):  # fmt: skip
         mlp = dict(kind="moe", expert=dict(ff=ff_size, limit=limit), router=dict(experts=E, top=top, scale=1.7))
         if groups:
