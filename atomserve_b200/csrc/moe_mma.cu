@@ -1,8 +1,9 @@
 // The routed experts' products for bfloat16 on the tensor cores: the same grouped rows, tiles
 // and results as the CUDA-core kernels of moe.cu (which stay the float32 path and the fallback),
-// with mma.sync m16n8k16 (bfloat16 in, float32 accumulate). A block computes a 64 x 64 tile of
-// one expert's rows: four warps of 32 x 32 each, K in steps of 32 staged through shared memory,
-// the next step's global loads in flight while the current one is multiplied. Each output
+// with mma.sync m16n8k16 (bfloat16 in, float32 accumulate). A block computes a 64 x 64 or a
+// 128 x 64 tile of one expert's rows: warps of 32 x 32 each, K in steps of 32 brought to shared
+// memory by 16-byte cp.async into two buffers (the next step arriving while this one is
+// multiplied), fragments by ldmatrix. Each output
 // element is one float32 accumulator chain over k in ascending order, so a row's result does not
 // depend on which rows share its tile.
 //
@@ -15,7 +16,8 @@
 
 namespace {
 
-constexpr int BM = 64, BN = 64, BK = 32, LD = BK + 8;  // LD: row stride in shared memory, conflict-free for the fragment loads
+constexpr int BN = 64, BK = 32, LD = BK + 8;  // LD: row stride in shared memory, conflict-free for ldmatrix
+constexpr int kStages = 2;
 
 struct GroupedParams {
   void* out;
@@ -28,21 +30,36 @@ struct GroupedParams {
   float limit, slope, shift;
 };
 
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t* b) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-template <bool GLU>
-__global__ void __launch_bounds__(128)
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* row) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+__device__ __forceinline__ void copy16(void* dst, const void* src, bool real) {
+  // 16 bytes global -> shared without passing registers; `real` false writes zeros instead
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(real ? 16 : 0) : "memory");
+}
+
+// WM warps along the rows (2: tiles of 64 rows, 4 warps; 4: tiles of 128 rows, 8 warps), two along
+// the columns; a warp computes 32 x 32 (and the same of the up matrix with GLU).
+template <bool GLU, int WM>
+__global__ void __launch_bounds__(WM * 64)
 grouped_gemm_mma_kernel(const GroupedParams p) {
+  constexpr int BM = WM * 32, kThreads = WM * 64;
   asb::pdl_wait();
   asb::pdl_launch_dependents();
-  __shared__ __align__(16) __nv_bfloat16 xs[BM][LD];
-  __shared__ __align__(16) __nv_bfloat16 ws[BN][LD];
-  __shared__ __align__(16) __nv_bfloat16 us[GLU ? BN : 1][LD];
+  __shared__ __align__(16) __nv_bfloat16 xs[kStages][BM][LD];
+  __shared__ __align__(16) __nv_bfloat16 ws[kStages][BN][LD];
+  __shared__ __align__(16) __nv_bfloat16 us[GLU ? kStages : 1][GLU ? BN : 1][LD];
   __shared__ int src_row[BM];
   int tile = blockIdx.y, e = 0, begin = 0, count = 0;
   for (; e < p.E; ++e) {
@@ -61,34 +78,24 @@ grouped_gemm_mma_kernel(const GroupedParams p) {
   const int K = p.K, N = p.N;
   const __nv_bfloat16* w = p.w + (size_t)e * N * K;
   const __nv_bfloat16* w2 = GLU ? p.w2 + (size_t)e * N * K : nullptr;
-  // loads: 64 rows x 4 chunks of 8 values per operand tile; a thread takes chunk tid and tid + 128
-  const int lrow0 = tid >> 2, lrow1 = lrow0 + 32, lchunk = (tid & 3) * 8;
-  const int xr0 = src_row[lrow0], xr1 = src_row[lrow1];
-  const int wn0 = n0 + lrow0, wn1 = n0 + lrow1;
-  uint4 rx[2], rw[2], ru[2];
-  const uint4 zero = make_uint4(0, 0, 0, 0);
-  auto fetch = [&](int k0) {
-    const int k = k0 + lchunk;
-    const bool in = k < K;
-    rx[0] = (in && xr0 >= 0) ? *reinterpret_cast<const uint4*>(p.x + (size_t)xr0 * K + k) : zero;
-    rx[1] = (in && xr1 >= 0) ? *reinterpret_cast<const uint4*>(p.x + (size_t)xr1 * K + k) : zero;
-    rw[0] = (in && wn0 < N) ? *reinterpret_cast<const uint4*>(w + (size_t)wn0 * K + k) : zero;
-    rw[1] = (in && wn1 < N) ? *reinterpret_cast<const uint4*>(w + (size_t)wn1 * K + k) : zero;
-    if constexpr (GLU) {
-      ru[0] = (in && wn0 < N) ? *reinterpret_cast<const uint4*>(w2 + (size_t)wn0 * K + k) : zero;
-      ru[1] = (in && wn1 < N) ? *reinterpret_cast<const uint4*>(w2 + (size_t)wn1 * K + k) : zero;
+
+  // a stage: BM x 4 chunks of x, 64 x 4 of each weight tile, 16 bytes each, by cp.async
+  auto request = [&](int k0, int stage) {
+    for (int i = tid; i < BM * 4; i += kThreads) {
+      const int r = i >> 2, k = k0 + (i & 3) * 8;
+      const int xr = src_row[r];
+      const bool real = xr >= 0 && k < K;
+      copy16(&xs[stage][r][(i & 3) * 8], real ? p.x + (size_t)xr * K + k : p.x, real);
     }
-  };
-  auto stage = [&]() {
-    *reinterpret_cast<uint4*>(&xs[lrow0][lchunk]) = rx[0];
-    *reinterpret_cast<uint4*>(&xs[lrow1][lchunk]) = rx[1];
-    *reinterpret_cast<uint4*>(&ws[lrow0][lchunk]) = rw[0];
-    *reinterpret_cast<uint4*>(&ws[lrow1][lchunk]) = rw[1];
-    if constexpr (GLU) {
-      *reinterpret_cast<uint4*>(&us[lrow0][lchunk]) = ru[0];
-      *reinterpret_cast<uint4*>(&us[lrow1][lchunk]) = ru[1];
+    for (int i = tid; i < BN * 4; i += kThreads) {
+      const int r = i >> 2, k = k0 + (i & 3) * 8;
+      const bool real = n0 + r < N && k < K;
+      copy16(&ws[stage][r][(i & 3) * 8], real ? w + (size_t)(n0 + r) * K + k : w, real);
+      if constexpr (GLU) copy16(&us[stage][r][(i & 3) * 8], real ? w2 + (size_t)(n0 + r) * K + k : w2, real);
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
+
   const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;  // the warp's 32 x 32 corner of the tile
   const int g = lane >> 2, t = lane & 3;
   float acc[2][4][4], acc2[GLU ? 2 : 1][4][4];
@@ -101,39 +108,43 @@ grouped_gemm_mma_kernel(const GroupedParams p) {
         acc[i][j][c] = 0.f;
         if constexpr (GLU) acc2[i][j][c] = 0.f;
       }
-  fetch(0);
-  for (int k0 = 0; k0 < K; k0 += BK) {
-    __syncthreads();  // the previous step's fragments have been read
-    stage();
+  // ldmatrix rows. A: row lane % 16 of a 16-row tile, k block lane / 16. B: row (lane % 8) + 8 * (lane / 16)
+  // of a pair of 8-column tiles, k block (lane / 8) % 2.
+  const int a_row = wm + (lane & 15), a_col = (lane >> 4) * 8;
+  const int b_row = wn + (lane & 7) + ((lane >> 4) & 1) * 8, b_col = ((lane >> 3) & 1) * 8;
+
+  request(0, 0);
+  for (int k0 = 0, stage = 0; k0 < K; k0 += BK, stage ^= 1) {
+    if (k0 + BK < K) {
+      request(k0 + BK, stage ^ 1);  // that buffer was read two steps ago, before the barrier that ended the last step
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
     __syncthreads();
-    if (k0 + BK < K) fetch(k0 + BK);
 #pragma unroll
     for (int kk = 0; kk < BK; kk += 16) {
       uint32_t a[2][4];
+      ldmatrix_x4(a[0], &xs[stage][a_row][kk + a_col]);
+      ldmatrix_x4(a[1], &xs[stage][a_row + 16][kk + a_col]);
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int r = wm + i * 16 + g;
-        a[i][0] = *reinterpret_cast<const uint32_t*>(&xs[r][kk + 2 * t]);
-        a[i][1] = *reinterpret_cast<const uint32_t*>(&xs[r + 8][kk + 2 * t]);
-        a[i][2] = *reinterpret_cast<const uint32_t*>(&xs[r][kk + 2 * t + 8]);
-        a[i][3] = *reinterpret_cast<const uint32_t*>(&xs[r + 8][kk + 2 * t + 8]);
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int n = wn + j * 8 + g;
-        uint32_t b[2];
-        b[0] = *reinterpret_cast<const uint32_t*>(&ws[n][kk + 2 * t]);
-        b[1] = *reinterpret_cast<const uint32_t*>(&ws[n][kk + 2 * t + 8]);
-        mma_bf16(acc[0][j], a[0], b);
-        mma_bf16(acc[1][j], a[1], b);
+      for (int jp = 0; jp < 2; ++jp) {  // a pair of 8-column tiles per ldmatrix
+        uint32_t b[4];
+        ldmatrix_x4(b, &ws[stage][b_row + jp * 16][kk + b_col]);
+        mma_bf16(acc[0][2 * jp], a[0], b);
+        mma_bf16(acc[1][2 * jp], a[1], b);
+        mma_bf16(acc[0][2 * jp + 1], a[0], b + 2);
+        mma_bf16(acc[1][2 * jp + 1], a[1], b + 2);
         if constexpr (GLU) {
-          b[0] = *reinterpret_cast<const uint32_t*>(&us[n][kk + 2 * t]);
-          b[1] = *reinterpret_cast<const uint32_t*>(&us[n][kk + 2 * t + 8]);
-          mma_bf16(acc2[0][j], a[0], b);
-          mma_bf16(acc2[1][j], a[1], b);
+          ldmatrix_x4(b, &us[stage][b_row + jp * 16][kk + b_col]);
+          mma_bf16(acc2[0][2 * jp], a[0], b);
+          mma_bf16(acc2[1][2 * jp], a[1], b);
+          mma_bf16(acc2[0][2 * jp + 1], a[0], b + 2);
+          mma_bf16(acc2[1][2 * jp + 1], a[1], b + 2);
         }
       }
     }
+    __syncthreads();  // this stage has been read: the step after next may overwrite it
   }
 #pragma unroll
   for (int i = 0; i < 2; ++i)
@@ -163,7 +174,11 @@ grouped_gemm_mma_kernel(const GroupedParams p) {
     }
 }
 
-int row_tiles(int pairs, int E) { return pairs / BM + (pairs < E ? pairs : E); }
+// Tiles of 128 rows once the experts have 64 rows each on average; below that the tiles of 64
+// rows waste less of the tensor cores' work on rows that do not exist.
+bool tall(int pairs, int E) { return pairs >= 64 * E; }
+
+int row_tiles(int pairs, int E, int bm) { return pairs / bm + (pairs < E ? pairs : E); }
 
 bool aligned16(const void* a, const void* b, const void* c) {
   return (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) == 0;
@@ -182,9 +197,11 @@ extern "C" int asb_moe_glu_mma(void* hidden, const void* x, const int* row_token
   p.out = hidden; p.x = (const __nv_bfloat16*)x; p.row_token = row_token; p.offsets = offsets;
   p.w = (const __nv_bfloat16*)gate; p.w2 = (const __nv_bfloat16*)up;
   p.E = E; p.N = F; p.K = K; p.limit = limit; p.slope = slope; p.shift = shift;
-  dim3 grid((F + BN - 1) / BN, row_tiles(pairs, E));
+  const bool big = tall(pairs, E);
+  dim3 grid((F + BN - 1) / BN, row_tiles(pairs, E, big ? 128 : 64));
   if (grid.y > 65535) return asb::fail("moe_glu_mma: %d rows exceed the grid", pairs);
-  asb::launch(grouped_gemm_mma_kernel<true>, grid, 128, 0, stream, p);
+  if (big) asb::launch(grouped_gemm_mma_kernel<true, 4>, grid, 256, 0, stream, p);
+  else asb::launch(grouped_gemm_mma_kernel<true, 2>, grid, 128, 0, stream, p);
   return asb::check_launch("moe_glu_mma");
 }
 
@@ -196,8 +213,10 @@ extern "C" int asb_moe_down_mma(float* y, const void* hidden, const int* offsets
   p.out = y; p.x = (const __nv_bfloat16*)hidden; p.row_token = nullptr; p.offsets = offsets;
   p.w = (const __nv_bfloat16*)down; p.w2 = nullptr;
   p.E = E; p.N = N; p.K = F; p.limit = 0.f; p.slope = 1.f; p.shift = 0.f;
-  dim3 grid((N + BN - 1) / BN, row_tiles(pairs, E));
+  const bool big = tall(pairs, E);
+  dim3 grid((N + BN - 1) / BN, row_tiles(pairs, E, big ? 128 : 64));
   if (grid.y > 65535) return asb::fail("moe_down_mma: %d rows exceed the grid", pairs);
-  asb::launch(grouped_gemm_mma_kernel<false>, grid, 128, 0, stream, p);
+  if (big) asb::launch(grouped_gemm_mma_kernel<false, 4>, grid, 256, 0, stream, p);
+  else asb::launch(grouped_gemm_mma_kernel<false, 2>, grid, 128, 0, stream, p);
   return asb::check_launch("moe_down_mma");
 }
