@@ -143,6 +143,15 @@ latent_attention_mma_kernel(const LatentParams p) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
 
+  // the positions of the four rows whose scores this thread writes, once (a division each)
+  int row_pos[2][2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int rr = i * 16 + g + half * 8;
+      row_pos[i][half] = rr < num_rows ? pos0 + rr / gc : -1;
+    }
   const int* table = p.block_tables + (size_t)r * p.table_width;
   const bool vector = (Dk % 8 == 0) && (((uintptr_t)p.pages & 15) == 0);
   const int chunks = Dk / 8;
@@ -151,13 +160,20 @@ latent_attention_mma_kernel(const LatentParams p) {
   // keys outside the block's range filled with zeros; the tile after the one being multiplied is
   // always on its way. Other widths are copied element by element when their turn comes.
   auto request_tile = [&](int kt0, __nv_bfloat16* k_s) {
-    for (int i = threadIdx.x; i < KT * chunks; i += blockDim.x) {
-      const int jj = i / chunks, c = i - jj * chunks;
-      const int j = kt0 + jj;
-      const bool in = j >= key_lo && j < key_hi;
-      const __nv_bfloat16* src = in ? p.pages + ((size_t)table[j / p.bs] * p.bs + j % p.bs) * Dk + c * 8 : p.pages;
-      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(k_s + jj * LDK + c * 8);
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(in ? 16 : 0) : "memory");
+    // a warp fetches 8 of the tile's keys: lanes 0-7 look up where they lie (one division each a
+    // tile), then all lanes copy each key's chunks
+    const int jw = kt0 + warp * 8 + (lane & 7);
+    long long mine = -1;
+    if (jw >= key_lo && jw < key_hi) mine = (long long)table[jw / p.bs] * p.bs + jw % p.bs;
+#pragma unroll
+    for (int r8 = 0; r8 < 8; ++r8) {
+      const long long slot = __shfl_sync(0xffffffffu, mine, r8);
+      const __nv_bfloat16* src = slot >= 0 ? p.pages + (size_t)slot * Dk : p.pages;
+      __nv_bfloat16* dst = k_s + (warp * 8 + r8) * LDK;
+      for (int c = lane; c < chunks; c += 32) {
+        const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst + c * 8);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(slot >= 0 ? src + c * 8 : src), "r"(slot >= 0 ? 16 : 0) : "memory");
+      }
     }
   };
   const int first_tile = (key_lo / KT) * KT;
@@ -228,7 +244,7 @@ latent_attention_mma_kernel(const LatentParams p) {
           const int rr = i * 16 + g + (c >> 1) * 8;
           const int jj = warp * 8 + 2 * t + (c & 1);
           const int j = kt0 + jj;
-          const bool visible = rr < num_rows && block_of_key[jj] >= 0 && j <= pos0 + rr / gc;
+          const bool visible = j >= key_lo && j < key_hi && j <= row_pos[i][c >> 1];  // (no position for rows beyond the block's)
           s_s[rr * LDS + jj] = visible ? s[i][c] * p.scale : -INFINITY;
         }
     }

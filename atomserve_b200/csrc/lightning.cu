@@ -37,6 +37,7 @@ struct LightningParams {
   const float* decay;       // [H]
   int stride, q_off, k_off, v_off;
   int H, D, V, DS, act;
+  int dp_shift, cpb_shift;  // log2 of the padded rows DS * RPT and of the value columns a block
   int zero_init;  // 1: the state starts at zero and is only written (a segment's local state)
   int carry;      // 1: add each token's share of the state it started from instead of running the recurrence
 };
@@ -55,7 +56,7 @@ lightning_kernel(const LightningParams p) {
   float* ks = qs + kTokenTile * DP;       // [TT][DP]
   float* vs = ks + kTokenTile * DP;       // [TT][CPB]
   const int r = blockIdx.x, h = blockIdx.y;
-  const int ds = threadIdx.x % DS, cl = threadIdx.x / DS;
+  const int ds = threadIdx.x & (DS - 1), cl = threadIdx.x >> (7 - p.cpb_shift);  // DS and 128 / DS are powers of two
   const int col = blockIdx.z * CPB + cl;
   const int row_lo = p.req_q_start[r], row_hi = p.req_q_start[r + 1];
   const int slot = p.state_slots[r];
@@ -81,7 +82,7 @@ lightning_kernel(const LightningParams p) {
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int i = base + u * kThreads;
-        const int t = i / DP, d = i - t * DP;
+        const int t = i >> p.dp_shift, d = i - (t << p.dp_shift);
         qv[u] = kv[u] = 0.f;
         if (i < nt * DP && d < p.D) {
           const T* row = proj + (size_t)(t0 + t) * p.stride + h * p.D + d;
@@ -104,7 +105,7 @@ lightning_kernel(const LightningParams p) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const int i = base + u * kThreads;
-          const int t = i / CPB, c = blockIdx.z * CPB + (i - t * CPB);
+          const int t = i >> p.cpb_shift, c = blockIdx.z * CPB + (i - (t << p.cpb_shift));
           vv[u] = (i < nt * CPB && c < p.V) ? asb::to_float(proj[(size_t)(t0 + t) * p.stride + p.v_off + h * p.V + c]) : 0.f;
         }
 #pragma unroll
@@ -241,6 +242,10 @@ extern "C" int asb_lightning_attention(float* out, const void* proj, int stride,
   while (ds * rpt < D) ds <<= 1;
   if (ds > 32) return asb::fail("lightning_attention: key size %d exceeds %d", D, 32 * 64);
   p.DS = ds;
+  p.dp_shift = 0;
+  while ((1 << p.dp_shift) < ds * rpt) ++p.dp_shift;
+  p.cpb_shift = 0;
+  while ((1 << p.cpb_shift) < kThreads / ds) ++p.cpb_shift;
   if ((V + kThreads / ds - 1) / (kThreads / ds) > 65535) return asb::fail("lightning_attention: value size %d", V);
   ASB_DISPATCH_DTYPE(dtype, T, {
     if (rpt == 64) return launch<T, 64>(p, R, stream);
