@@ -65,6 +65,12 @@ __device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], const void* row) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
 }
 
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* row) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
 // NT: 8-column tiles of the output per warp; the block covers 64 * NT >= rank columns
 template <int NT>
 __global__ void __launch_bounds__(kWarps * 32)
@@ -212,6 +218,7 @@ latent_attention_mma_kernel(const LatentParams p) {
       const __nv_bfloat16* kb = k_s + (warp * 8 + (lane & 7)) * LDK + (lane >> 3) * 8;
       int kk = 0;
       float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};  // odd k steps: four chains of dependent MMAs, not two
+#pragma unroll 2
       for (; kk + 32 <= DKP; kk += 32) {
         uint32_t b4[4], a0[4], a1[4], a2[4], a3[4];
         ldmatrix_x4(b4, kb + kk);
@@ -291,20 +298,25 @@ latent_attention_mma_kernel(const LatentParams p) {
 #pragma unroll
       for (int kk = 0; kk < KT; kk += 16) {
         uint32_t a[2][4];
+        ldmatrix_x4(a[0], p_s + (lane & 15) * LDP + kk + (lane >> 4) * 8);
+        ldmatrix_x4(a[1], p_s + (16 + (lane & 15)) * LDP + kk + (lane >> 4) * 8);
+        if constexpr (NT >= 2) {
+          // two 8-column tiles per ldmatrix: keys kk + lane % 16, columns of tile j + lane / 16
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const __nv_bfloat16* pa = p_s + (i * 16 + g) * LDP + kk + 2 * t;
-          a[i][0] = *reinterpret_cast<const uint32_t*>(pa);
-          a[i][1] = *reinterpret_cast<const uint32_t*>(pa + 8 * LDP);
-          a[i][2] = *reinterpret_cast<const uint32_t*>(pa + 8);
-          a[i][3] = *reinterpret_cast<const uint32_t*>(pa + 8 * LDP + 8);
-        }
-#pragma unroll
-        for (int j = 0; j < NT; ++j) {
+          for (int j = 0; j < NT; j += 2) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, k_s + (kk + (lane & 15)) * LDK + col0 + (j + (lane >> 4)) * 8);
+            const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
+            mma_bf16(acc[0][j], a[0], b0);
+            mma_bf16(acc[1][j], a[1], b0);
+            mma_bf16(acc[0][j + 1], a[0], b1);
+            mma_bf16(acc[1][j + 1], a[1], b1);
+          }
+        } else {
           uint32_t b[2];
-          ldmatrix_x2_trans(b, k_s + (kk + (lane & 15)) * LDK + col0 + j * 8);
-          mma_bf16(acc[0][j], a[0], b);
-          mma_bf16(acc[1][j], a[1], b);
+          ldmatrix_x2_trans(b, k_s + (kk + (lane & 15)) * LDK + col0);
+          mma_bf16(acc[0][0], a[0], b);
+          mma_bf16(acc[1][0], a[1], b);
         }
       }
     }
