@@ -72,7 +72,8 @@ def engine_config_for(args: argparse.Namespace, model, max_positions: int) -> En
     """Size the cache pool from the memory budget; cap the sequence length by pool and model
     (atomserve/cli.py:99-119)."""
     block_bytes = CacheManager.bytes_per_block(model.cache_requirements(), args.block_size, DTYPES[args.dtype])
-    num_blocks = int(args.kv_mem_gb * 2**30 // block_bytes)
+    # (a model that keeps nothing in pages, only fixed-size state, needs no pool to speak of)
+    num_blocks = int(args.kv_mem_gb * 2**30 // block_bytes) if block_bytes else max(1, max_positions // args.block_size)
     return EngineConfig(
         block_size=args.block_size,
         num_blocks=num_blocks,

@@ -125,6 +125,9 @@ class StepContext:
     host_q_lens: list[int] = field(default_factory=list)
     host_pos_start: list[int] = field(default_factory=list)
     host_state_slots: list[int] = field(default_factory=list)
+    # what a part works out once per step for all layers of its kind (a cut of the step's requests
+    # into segments, say), under a name of the part's choosing
+    plans: dict[str, Any] = field(default_factory=dict)
 
 
 # ---- interfaces -----------------------------------------------------------------------------

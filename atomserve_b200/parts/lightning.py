@@ -55,11 +55,11 @@ class LightningAttention(Mixer):
         proj = ops.linear(h, self.in_proj)
         # long portions are cut into segments that run side by side; the cut is made once per step
         # and shared by the step's layers
-        if not hasattr(ctx, "lightning_segments"):
-            ctx.lightning_segments = ops.plan_segments(ctx.host_q_lens, h.device) if ctx.host_q_lens else None
+        if "lightning_segments" not in ctx.plans:
+            ctx.plans["lightning_segments"] = ops.plan_segments(ctx.host_q_lens, h.device) if ctx.host_q_lens else None
         o = ops.lightning_attention(proj, 0, qk, 2 * qk, cache.state["s"], ctx.state_slots, ctx.req_q_start, self.decay,
                                     ctx.num_requests, activation=self.activation == "silu",
-                                    segments=ctx.lightning_segments)  # fmt: skip
+                                    segments=ctx.plans["lightning_segments"])  # fmt: skip
         gated = ops.gated_rms_norm(o, proj[:, 2 * qk + vg :], self.gain, self.eps)
         # without a residual (a block that sums in float32 itself) the product stays float32
         return ops.linear(gated, self.o_proj, residual, out_dtype=torch.float32 if residual is None else None)
