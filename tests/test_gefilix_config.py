@@ -62,3 +62,37 @@ def broken(change):
 def test_rejections(change):
     with pytest.raises(ModelConfigError):
         config_from_dict(broken(change))
+
+
+def test_segments_of_a_step():
+    """Requests of 256 tokens and more are cut into segments of 64; shorter ones stay whole."""
+    import torch
+
+    from atomserve_b200.ops.recurrent import SEGMENT_FROM, SEGMENT_TOKENS, plan_segments
+
+    assert plan_segments([1, SEGMENT_FROM - 1], torch.device("cpu")) is None
+    lens = [300, 1, 5, SEGMENT_FROM]
+    seg = plan_segments(lens, torch.device("cpu"))
+    bounds, starts = seg.bounds.tolist(), seg.req_start.tolist()
+    assert bounds[0] == 0 and bounds[-1] == sum(lens) and seg.count == len(bounds) - 1
+    assert all(0 < b - a <= SEGMENT_TOKENS or (b - a) in lens for a, b in zip(bounds, bounds[1:]))
+    row = 0
+    for r, n in enumerate(lens):  # each request's segments tile its rows exactly
+        assert bounds[starts[r]] == row and bounds[starts[r + 1]] == row + n
+        row += n
+    assert seg.index.tolist() == list(range(seg.count))
+
+
+def test_state_buffers_have_a_row_that_belongs_to_no_request():
+    import torch
+
+    from atomserve_b200.cache.state_slots import StateSlots
+
+    slots = StateSlots(3)
+    buf = slots.register("s", (2, 2), torch.float32)
+    assert buf.shape == (4, 2, 2) and slots.pad_slot == 3
+    taken = [slots.take() for _ in range(3)]
+    assert sorted(taken) == [0, 1, 2] and slots.num_free == 0
+    buf[1] = 7.0
+    slots.give_back(1)
+    assert slots.take() == 1 and not buf[1].any()  # zeroed when handed out again

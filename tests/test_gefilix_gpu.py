@@ -225,7 +225,7 @@ def test_expert_selection():
     from atomserve_b200 import ops
 
     g = torch.Generator().manual_seed(3)
-    for E, top, groups, scale in ((16, 4, (2, 1), 2.5), (6, 2, (3, 2), 1.7), (4, 1, None, 1.0), (8, 3, (2, 2), 2.0),
+    for E, top, groups, scale in ((18, 3, (3, 1), 2.2), (6, 2, (3, 2), 1.7), (4, 1, None, 1.0), (8, 3, (2, 2), 2.0),
                                   (5, 5, None, 0.5), (12, 3, (12, 4), 1.0), (64, 8, (8, 3), 1.3), (40, 32, None, 1.0)):  # fmt: skip
         z = torch.randn(33, E + 1, generator=g) * 2
         router = dict(experts=E, top=top, scale=scale)
@@ -263,7 +263,7 @@ def test_feed_forwards_alone(dtype):
     check(out, plain.dense_feed_forward({k: v.double() for k, v in w.items()}, "f.", h.double()).float(), dtype, "dense", 0.02)
     # routed experts of three kinds; equal inputs, so selection is the oracle's in bfloat16 too
     for E, top, groups, ff_size, limit, shared in ((6, 2, (3, 2), 48, 1.5, (32, 3.0)), (4, 1, None, 36, 0.5, None),
-                                                   (16, 4, (2, 1), 72, 2.0, (24, 1.0))):  # fmt: skip
+                                                   (15, 4, (3, 2), 72, 1.8, (24, 1.0))):  # fmt: skip
         mlp = dict(kind="moe", expert=dict(ff=ff_size, limit=limit), router=dict(experts=E, top=top, scale=1.7))
         if groups:
             mlp["router"]["groups"] = dict(count=groups[0], keep=groups[1])

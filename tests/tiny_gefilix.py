@@ -60,7 +60,7 @@ GEFILIX_C = dict(
     layers=[
         dict(_lightning(4, 128, 64, [0.6, 0.9, 0.99, 0.999]), mlp=_moe(8, 2, 128, 2.0, 2.5, groups=(4, 2), shared=(64, 2.0))),
         dict(_latent(4, 64, 32, 64, 96, 0.35, base=100000.0), mlp=dict(kind="dense", ff=512)),
-        dict(_lightning(5, 64, 128, [0.7, 0.8, 0.9, 0.95, 1.0]), mlp=_moe(16, 4, 64, 1.0, 1.5, groups=(2, 1), shared=(128, 1.5))),
+        dict(_lightning(5, 64, 128, [0.7, 0.8, 0.9, 0.95, 1.0]), mlp=_moe(12, 3, 64, 1.0, 1.5, groups=(3, 1), shared=(128, 1.5))),
         dict(_latent(8, 32, 32, 32, 96, 0.5, base=100000.0, kv_from=1), mlp=dict(kind="dense", ff=256)),
     ],
 )  # fmt: skip
