@@ -19,7 +19,7 @@ class Rotary(PositionEncoding):
             raise ValueError(f"pairing {pairing!r} is neither 'half' nor 'interleaved'")
         self.pairing = pairing
         self.head_dim = head_dim
-        self.rotary_dim = rotary_dim or head_dim
+        self.rotary_dim = head_dim if rotary_dim is None else rotary_dim  # (0: nothing turns)
         if self.rotary_dim % 2 or self.rotary_dim > head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {head_dim}")
         self.theta = float(theta)
