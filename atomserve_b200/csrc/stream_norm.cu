@@ -11,6 +11,7 @@
 //
 // Sums, norms and gates are float32; each stored value is rounded once.
 #include "common.cuh"
+#include "gemm_partials.cuh"
 
 namespace {
 
@@ -85,6 +86,50 @@ __global__ void gated_rmsnorm_kernel(T* __restrict__ out, const float* __restric
   }
 }
 
+// The same with y given as the partial sums that the tensor-core GEMM left in its workspace (few
+// tokens): a thread adds up the slots of 8 columns itself, so the GEMM's reduction kernel and a
+// round trip of y through memory fall away. The slots are added in the reduction's order; only a
+// row's squares are added in another order than in the kernel above (8 neighbouring columns a thread).
+__global__ void partial_scaled_add_rmsnorm_kernel(float* __restrict__ out32, __nv_bfloat16* __restrict__ out_c,
+                                                  const asb::PartialSums ps, const float* __restrict__ x,
+                                                  const float* __restrict__ gain, int width, float alpha, float eps) {
+  __shared__ float scratch[32];
+  const int t = blockIdx.x, i = threadIdx.x * 8;
+  const bool active = i < width;
+  const int slots = active ? asb::partial_slots(ps, i / asb::kPartialRows) : 0;
+  asb::pdl_wait();
+  asb::pdl_launch_dependents();
+  float v[8];
+  float ss = 0.f;
+  if (active) {
+    float sum[8];
+    asb::partial_sum<8>(ps, t, i, slots, sum);
+    const float4 x0 = *reinterpret_cast<const float4*>(x + (size_t)t * width + i);
+    const float4 x1 = *reinterpret_cast<const float4*>(x + (size_t)t * width + i + 4);
+    const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      v[k] = fmaf(alpha, xs[k], sum[k]);
+      ss = fmaf(v[k], v[k], ss);
+    }
+  }
+  ss = asb::block_sum(ss, scratch);
+  if (!active) return;
+  const float inv = 1.f / sqrtf(ss / (float)width + eps);
+  const float4 g0 = *reinterpret_cast<const float4*>(gain + i), g1 = *reinterpret_cast<const float4*>(gain + i + 4);
+  const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+  uint4 packed;
+  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&packed);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    v[k] = v[k] * inv * g[k];
+    o[k] = __float2bfloat16_rn(v[k]);
+  }
+  *reinterpret_cast<float4*>(out32 + (size_t)t * width + i) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(out32 + (size_t)t * width + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  *reinterpret_cast<uint4*>(out_c + (size_t)t * width + i) = packed;
+}
+
 int threads_for(int width) { return width >= 4096 ? 512 : (width >= 1024 ? 256 : 128); }
 
 }  // namespace
@@ -130,4 +175,25 @@ extern "C" int asb_gated_rmsnorm(void* out, const float* o, const void* gate, in
   ASB_DISPATCH_DTYPE(dtype, T, asb::launch(gated_rmsnorm_kernel<T>, n, threads_for(width), 0, stream, (T*)out, o,
                                            (const T*)gate, gate_stride, gain, width, eps));
   return asb::check_launch("gated_rmsnorm");
+}
+
+// out32 (float32) and out_c (bfloat16) = RMSNorm(alpha x + y), y being the partial sums of
+// asb_gemm_tcgen05 mode 3 on [tokens, K] x [width, K]. Widths that are a multiple of 8 up to 8192,
+// pointers 16-byte aligned.
+extern "C" int asb_partial_scaled_add_rmsnorm(float* out32, void* out_c, const float* ws, int max_slots, int bn,
+                                              int kb_per_tile, int num_tiles, int blocks, const float* x,
+                                              const float* gain, int tokens, int width, float alpha, float eps,
+                                              cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (width % 8 || width / 8 > 1024) return asb::fail("partial_scaled_add_rmsnorm: width %d must be a multiple of 8 up to 8192", width);
+  if (tokens > bn || num_tiles * asb::kPartialRows < width)
+    return asb::fail("partial_scaled_add_rmsnorm: %d tokens x %d columns do not fit the partial sums (%d x %d)", tokens, width, bn,
+                     num_tiles * asb::kPartialRows);
+  if (((uintptr_t)out32 | (uintptr_t)out_c | (uintptr_t)x | (uintptr_t)gain | (uintptr_t)ws) & 15)
+    return asb::fail("partial_scaled_add_rmsnorm: pointers must be 16-byte aligned");
+  const asb::PartialSums ps = {ws, max_slots, bn, kb_per_tile, num_tiles, blocks};
+  const int threads = ((width / 8) + 31) / 32 * 32;
+  asb::launch(partial_scaled_add_rmsnorm_kernel, tokens, threads, 0, stream, out32, (__nv_bfloat16*)out_c, ps, x, gain, width,
+              alpha, eps);
+  return asb::check_launch("partial_scaled_add_rmsnorm");
 }

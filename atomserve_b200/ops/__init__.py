@@ -20,11 +20,11 @@ from atomserve_b200.ops.recurrent import lightning_attention, plan_segments
 from atomserve_b200.ops.linear import PartialSums, interleave_gate_up, linear, linear_partial, linear_swiglu, swiglu_fusable
 from atomserve_b200.ops.sampling import argmax_rows, presence_penalty, sample_rows
 from atomserve_b200.ops.status import DeviceStatus, status_for
-from atomserve_b200.ops.stream import cast_rows, clamped_glu, embedding_scaled, gated_rms_norm, gelu, scaled_add_rms_norm
+from atomserve_b200.ops.stream import cast_rows, clamped_glu, embedding_scaled, gated_rms_norm, gelu, linear_for_stream, scaled_add_rms_norm
 
 __all__ = [
     "cast_rows", "clamped_glu", "combine", "embedding_scaled", "experts_down", "experts_glu", "gated_rms_norm", "gelu",
-    "group_by_expert", "head_matmul", "head_matmul_on_tensor_cores", "latent_attention", "latent_prepare", "lightning_attention", "plan_segments", "route",
+    "group_by_expert", "linear_for_stream", "head_matmul", "head_matmul_on_tensor_cores", "latent_attention", "latent_prepare", "lightning_attention", "plan_segments", "route",
     "scaled_add_rms_norm",
     "DeviceStatus",
     "KernelLibraryError",

@@ -52,6 +52,7 @@ _SIGNATURES = {
     "asb_cast_rows": [_P, _P, ctypes.c_longlong, _I, _P],
     "asb_scaled_add_rmsnorm": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _F, _F, _I, _P],
     "asb_gated_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _I, _P],
+    "asb_partial_scaled_add_rmsnorm": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _I, _I, _F, _F, _P],
     "asb_gelu": [_P, _P, ctypes.c_longlong, _I, _I, _P],
     "asb_clamped_glu": [_P, _P, _I, _I, _F, _F, _F, _I, _P],
     # linear attention with a decay per head

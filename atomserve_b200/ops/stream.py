@@ -6,6 +6,7 @@ from __future__ import annotations
 import torch
 
 from atomserve_b200.ops.library import KernelLibraryError, check, dtype_code, lib, ptr, require_cuda, stream
+from atomserve_b200.ops.linear import PartialSums, linear, linear_partial
 
 
 def _stream(x: torch.Tensor, name: str) -> None:
@@ -35,12 +36,23 @@ def cast_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     return out
 
 
-def scaled_add_rms_norm(x: torch.Tensor, y: torch.Tensor | None, alpha: float, gain: torch.Tensor, eps: float,
+def scaled_add_rms_norm(x: torch.Tensor, y: torch.Tensor | PartialSums | None, alpha: float, gain: torch.Tensor, eps: float,
                         dtype: torch.dtype, rows: torch.Tensor | None = None,
                         want_stream: bool = True) -> tuple[torch.Tensor | None, torch.Tensor]:  # fmt: skip
     """s = alpha x + y (y absent: alpha x); n = gain * s / sqrt(mean(s^2) + eps). x: float32
-    [N, width]; y: float32 or bfloat16; `rows` (int32) picks source rows. Returns (n as float32 or
+    [N, width]; y: float32 or bfloat16, or the partial sums of a product (`linear_for_stream`),
+    which the kernel then adds up itself; `rows` (int32) picks source rows. Returns (n as float32 or
     None, n in `dtype`); with dtype float32 both are one tensor."""
+    if isinstance(y, PartialSums):
+        require_cuda(x, gain)
+        _stream(x, "x")
+        if rows is not None or dtype != torch.bfloat16 or (y.tokens, y.columns) != tuple(x.shape) or gain.shape != (x.shape[1],):
+            raise KernelLibraryError("partial sums are added to all rows of a stream of their shape, for bfloat16 products")
+        out32 = torch.empty_like(x)
+        out_c = torch.empty_like(x, dtype=dtype)
+        check(lib().asb_partial_scaled_add_rmsnorm(ptr(out32), ptr(out_c), ptr(y.workspace), *y.layout(), ptr(x), ptr(gain),
+                                                   x.shape[0], x.shape[1], float(alpha), float(eps), stream()))  # fmt: skip
+        return out32, out_c
     require_cuda(x, y, gain, rows)
     _stream(x, "x")
     width = x.shape[1]
@@ -55,6 +67,18 @@ def scaled_add_rms_norm(x: torch.Tensor, y: torch.Tensor | None, alpha: float, g
                                        ptr(rows), n, width, float(alpha), float(eps),
                                        dtype_code(out_c) if out_c is not None else 0, stream()))  # fmt: skip
     return out32, (out32 if out_c is None else out_c)
+
+
+def linear_for_stream(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor | PartialSums:
+    """x . w^T for a block that adds it to a float32 stream and norms the sum: float32, or, where
+    the tensor-core GEMM runs with partial sums (few tokens) and `scaled_add_rms_norm` can read
+    them, those partial sums. They live in the GEMMs' shared workspace, so the sum and norm must
+    follow at once."""
+    if w.shape[0] % 8 == 0 and w.shape[0] <= 8192:
+        product = linear_partial(x, w)
+        if product is not None:
+            return product
+    return linear(x, w, out_dtype=torch.float32)
 
 
 def gated_rms_norm(o: torch.Tensor, gate: torch.Tensor, gain: torch.Tensor, eps: float) -> torch.Tensor:

@@ -53,9 +53,14 @@ class PostNormBlock(Block):
     def forward_chain(self, x: torch.Tensor, normed: torch.Tensor | None, ctx: StepContext, cache: CacheView | None,
                       write_cache: bool, then: Norm | None) -> tuple[torch.Tensor, torch.Tensor | None]:  # fmt: skip
         h = normed if normed is not None else ops.cast_rows(x, self.dtype)
-        x, h = self.mixer_norm.add_forward(x, self.mixer.forward(h, None, ctx, cache, write_cache))
+        # a sublayer that offers `forward_for_stream` may hand its last product over as the GEMM's
+        # partial sums, which the norm's kernel then adds up itself (nothing runs in between)
+        mix = getattr(self.mixer, "forward_for_stream", None)
+        y = mix(h, ctx, cache, write_cache) if mix is not None else self.mixer.forward(h, None, ctx, cache, write_cache)
+        x, h = self.mixer_norm.add_forward(x, y)
         if self.has_feed_forward:
-            x, h = self.feed_forward_norm.add_forward(x, self.feed_forward.forward(h, None, ctx))
+            ff = getattr(self.feed_forward, "forward_for_stream", None)
+            x, h = self.feed_forward_norm.add_forward(x, ff(h, ctx) if ff is not None else self.feed_forward.forward(h, None, ctx))
         return x, h
 
 

@@ -19,11 +19,6 @@ from atomserve_b200.parts.base import FeedForward, StepContext, register_part
 from atomserve_b200.parts.spec import TensorSpec
 
 
-def _out_dtype(residual: torch.Tensor | None) -> torch.dtype | None:
-    # without a residual (a block that sums in float32 itself) the last product stays float32
-    return torch.float32 if residual is None else None
-
-
 class GeluMLP(FeedForward):
     """down(gelu(up h)), the exact (erf) GELU or its tanh form; no biases."""
 
@@ -39,7 +34,14 @@ class GeluMLP(FeedForward):
         self.up, self.down = tensors[self.prefix + "up"], tensors[self.prefix + "down"]
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor | None, ctx: StepContext) -> torch.Tensor:
-        return ops.linear(ops.gelu(ops.linear(h, self.up), self.tanh_form), self.down, residual, out_dtype=_out_dtype(residual))
+        inner = ops.gelu(ops.linear(h, self.up), self.tanh_form)
+        # without a residual (a block that sums in float32 itself) the product stays float32
+        return ops.linear(inner, self.down, residual, out_dtype=torch.float32 if residual is None else None)
+
+    def forward_for_stream(self, h: torch.Tensor, ctx: StepContext):
+        """ff(h) for a block that adds it to a float32 stream and norms the sum at once: float32, or
+        the down projection's partial sums for that norm to add up (`ops.linear_for_stream`)."""
+        return ops.linear_for_stream(ops.gelu(ops.linear(h, self.up), self.tanh_form), self.down)
 
 
 class RoutedExperts(FeedForward):

@@ -76,6 +76,17 @@ class LatentAttention(Mixer):
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor | None, ctx: StepContext,
                 cache: CacheView | None, write_cache: bool = True) -> torch.Tensor:  # fmt: skip
+        # without a residual (a block that sums in float32 itself) the product stays float32
+        return ops.linear(self.mixed(h, ctx, cache, write_cache), self.o_proj, residual,
+                          out_dtype=torch.float32 if residual is None else None)  # fmt: skip
+
+    def forward_for_stream(self, h: torch.Tensor, ctx: StepContext, cache: CacheView | None, write_cache: bool = True):
+        """mix(h) for a block that adds it to a float32 stream and norms the sum at once: float32, or
+        the output projection's partial sums for that norm to add up (`ops.linear_for_stream`)."""
+        return ops.linear_for_stream(self.mixed(h, ctx, cache, write_cache), self.o_proj)
+
+    def mixed(self, h: torch.Tensor, ctx: StepContext, cache: CacheView | None, write_cache: bool) -> torch.Tensor:
+        """The gated heads' outputs side by side, [T, heads * vdim], before the output projection."""
         if write_cache == self.reads_only:
             raise ValueError("a latent attention without a down-projection reads another entry's pages, one with it its own")
         T, H, D, Rt, V, R = h.shape[0], self.heads, self.dim, self.rot_dim, self.vdim, self.kv_rank
@@ -92,8 +103,7 @@ class LatentAttention(Mixer):
                                      num_requests=ctx.num_requests, max_context=ctx.max_context, scale=self.scale)  # fmt: skip
         out = torch.empty(T, H * V, device=h.device, dtype=h.dtype)
         ops.head_matmul(mixed, self.uv_t, out.view(T, H, V), gate=proj[:, gate_off : gate_off + H], w_is_nk=self.uv_nk)
-        # without a residual (a block that sums in float32 itself) the product stays float32
-        return ops.linear(out, self.o_proj, residual, out_dtype=torch.float32 if residual is None else None)
+        return out
 
 
 register_part("mixer", "latent_attention", LatentAttention)

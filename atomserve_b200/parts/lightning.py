@@ -49,8 +49,8 @@ class LightningAttention(Mixer):
         self.o_proj, self.gain = tensors[p + "o"], tensors[p + "norm"]
         self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=self.o_proj.device)
 
-    def forward(self, h: torch.Tensor, residual: torch.Tensor | None, ctx: StepContext,
-                cache: CacheView | None, write_cache: bool = True) -> torch.Tensor:  # fmt: skip
+    def mixed(self, h: torch.Tensor, ctx: StepContext, cache: CacheView | None) -> torch.Tensor:
+        """The gated, normed heads side by side, [T, heads * vdim], before the output projection."""
         qk, vg = self.heads * self.dim, self.heads * self.vdim
         proj = ops.linear(h, self.in_proj)
         # long portions are cut into segments that run side by side; the cut is made once per step
@@ -60,9 +60,17 @@ class LightningAttention(Mixer):
         o = ops.lightning_attention(proj, 0, qk, 2 * qk, cache.state["s"], ctx.state_slots, ctx.req_q_start, self.decay,
                                     ctx.num_requests, activation=self.activation == "silu",
                                     segments=ctx.plans["lightning_segments"])  # fmt: skip
-        gated = ops.gated_rms_norm(o, proj[:, 2 * qk + vg :], self.gain, self.eps)
+        return ops.gated_rms_norm(o, proj[:, 2 * qk + vg :], self.gain, self.eps)
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor | None, ctx: StepContext,
+                cache: CacheView | None, write_cache: bool = True) -> torch.Tensor:  # fmt: skip
         # without a residual (a block that sums in float32 itself) the product stays float32
-        return ops.linear(gated, self.o_proj, residual, out_dtype=torch.float32 if residual is None else None)
+        return ops.linear(self.mixed(h, ctx, cache), self.o_proj, residual, out_dtype=torch.float32 if residual is None else None)
+
+    def forward_for_stream(self, h: torch.Tensor, ctx: StepContext, cache: CacheView | None, write_cache: bool = True):
+        """mix(h) for a block that adds it to a float32 stream and norms the sum at once: float32, or
+        the output projection's partial sums for that norm to add up (`ops.linear_for_stream`)."""
+        return ops.linear_for_stream(self.mixed(h, ctx, cache), self.o_proj)
 
 
 register_part("mixer", "lightning_attention", LightningAttention)

@@ -60,6 +60,30 @@ def test_norm_after_the_sum_and_the_scaled_embedding(dtype):
     check(out, table[[4, 49, 0, 4]] * 0.3, torch.float32, "scaled embedding")
 
 
+def test_norm_after_the_sum_reading_a_products_partial_sums():
+    """With few tokens the last product of a sublayer stays as the GEMM's partial sums and the
+    norm's kernel adds them up: the finished product followed by the norm, up to the order in
+    which a row's squares are added (a few float32 ulps; the bfloat16 copy within one of its own)."""
+    from atomserve_b200 import ops
+    from atomserve_b200.ops.linear import PartialSums
+
+    g = torch.Generator().manual_seed(4)
+    met = 0
+    for T, d, K in ((1, 256, 512), (5, 320, 1024), (8, 2048, 2048), (33, 256, 384)):
+        inner = (torch.randn(T, K, generator=g)).bfloat16().cuda()
+        w = (torch.randn(d, K, generator=g) * K**-0.5).bfloat16().cuda()
+        x = torch.randn(T, d, generator=g).cuda()
+        gain = (1 + 0.1 * torch.randn(d, generator=g)).cuda()
+        whole = ops.scaled_add_rms_norm(x, ops.linear(inner, w, out_dtype=torch.float32), 1.7, gain, EPS, torch.bfloat16)
+        y = ops.linear_for_stream(inner, w)
+        met += isinstance(y, PartialSums)
+        fused = ops.scaled_add_rms_norm(x, y, 1.7, gain, EPS, torch.bfloat16)
+        what = f"{T} tokens, width {d}, K {K}"
+        assert float((whole[0] - fused[0]).abs().max() / whole[0].abs().max()) < 2e-6, what
+        assert bool(((whole[1].float() - fused[1].float()).abs() <= 2.0**-7 * whole[1].float().abs() + 1e-30).all()), what
+    assert met, "no shape ran with partial sums"
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,D,V", [(3, 24, 40), (2, 96, 20), (1, 16, 16), (4, 64, 64), (2, 160, 130), (5, 8, 3)])
 def test_lightning_attention_alone(dtype, H, D, V):
