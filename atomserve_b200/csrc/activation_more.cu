@@ -2,6 +2,7 @@
 //
 //   asb_gelu          out = 0.5 z (1 + erf(z / sqrt 2))            (tanh_form 0, the exact GELU)
 //                     out = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))       (tanh_form 1)
+//                     out = max(z, 0)^2                            (tanh_form 2, the squared ReLU)
 //   asb_clamped_glu   gu = [T, 2F], gate columns first: g = min(gate, limit),
 //                     u = clamp(up, -limit, limit), out = g sigmoid(slope g) (u + shift)
 //                     (limit <= 0: no clamping)
@@ -22,7 +23,8 @@ __global__ void gelu_kernel(T* __restrict__ out, const T* __restrict__ in, long 
   asb::pdl_launch_dependents();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const float z = asb::to_float(in[i]);
-    out[i] = asb::from_float<T>(tanh_form ? asb::gelu_tanh(z) : asb::gelu_erf(z));
+    const float r = fmaxf(z, 0.f);
+    out[i] = asb::from_float<T>(tanh_form == 2 ? r * r : (tanh_form ? asb::gelu_tanh(z) : asb::gelu_erf(z)));
   }
 }
 

@@ -41,6 +41,8 @@ struct AttentionParams {
   float* part_m;             // [T, H, NP]      (NP > 1 only)
   float* part_l;             // [T, H, NP]
   float* part_acc;           // [T, H, NP, hd]
+  const float* sink;         // [H] or null: a logit per head that joins the softmax's denominator
+                             // once, unscaled, with no key and no value
   int R, H, KV, hd, bs, table_width;
   int QT, GC, HC;            // tokens per tile, heads per chunk, chunks per kv head
   int window;                // 0: none
@@ -163,6 +165,22 @@ paged_attention_kernel(const AttentionParams p) {
           if (col < hd) acc[s][e] = fmaf(w, v_s[jj * hd + col], acc[s][e]);
         }
       }
+    }
+  }
+
+  // The sink counts once per row: in the row's first partition.
+  if (p.sink && blockIdx.z == 0) {
+#pragma unroll
+    for (int s = 0; s < kRowsPerWarp; ++s) {
+      const int rr = warp + s * kWarps;
+      if (rr >= num_rows) break;
+      const float sk = p.sink[head0 + rr % gc];
+      const float m_new = fmaxf(m[s], sk);
+      const float corr = expf(m[s] - m_new);  // 0 for a row that has seen no key yet
+      l[s] = l[s] * corr + expf(sk - m_new);
+      m[s] = m_new;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) acc[s][e] *= corr;
     }
   }
 
@@ -341,13 +359,13 @@ extern "C" void asb_attention_tile_shape(int G, int* QT, int* GC) {
 
 // Float scratch needed when NP > 1: part_m and part_l take T*H*NP floats each, part_acc
 // T*H*NP*hd. Every partition slot of every row is written before the reduction reads it.
-extern "C" int asb_paged_attention(void* out, const void* q, const void* k_cache,
-                                   const void* v_cache, const int* block_tables,
-                                   const int* req_q_start, const int* req_pos_start,
-                                   float* part_m, float* part_l, float* part_acc,
-                                   int num_tokens, int R, int H, int KV, int hd, int bs,
-                                   int table_width, int window, int PS, int NP, float scale,
-                                   int dtype, cudaStream_t stream) {
+extern "C" int asb_paged_attention_sink(void* out, const void* q, const void* k_cache,
+                                        const void* v_cache, const int* block_tables,
+                                        const int* req_q_start, const int* req_pos_start,
+                                        float* part_m, float* part_l, float* part_acc, const float* sink,
+                                        int num_tokens, int R, int H, int KV, int hd, int bs,
+                                        int table_width, int window, int PS, int NP, float scale,
+                                        int dtype, cudaStream_t stream) {
   if (num_tokens == 0 || R == 0) return 0;
   if (KV < 1 || H % KV) return asb::fail("paged_attention: %d heads over %d kv heads", H, KV);
   if (hd < 1 || hd > 256) return asb::fail("paged_attention: head_dim %d not in 1..256", hd);
@@ -357,7 +375,7 @@ extern "C" int asb_paged_attention(void* out, const void* q, const void* k_cache
   AttentionParams p;
   p.q = q; p.out = out; p.k_cache = k_cache; p.v_cache = v_cache;
   p.block_tables = block_tables; p.req_q_start = req_q_start; p.req_pos_start = req_pos_start;
-  p.part_m = part_m; p.part_l = part_l; p.part_acc = part_acc;
+  p.part_m = part_m; p.part_l = part_l; p.part_acc = part_acc; p.sink = sink;
   p.R = R; p.H = H; p.KV = KV; p.hd = hd; p.bs = bs; p.table_width = table_width;
   asb_attention_tile_shape(H / KV, &p.QT, &p.GC);
   p.HC = (H / KV + p.GC - 1) / p.GC;
@@ -365,4 +383,16 @@ extern "C" int asb_paged_attention(void* out, const void* q, const void* k_cache
   p.window = window; p.PS = PS; p.NP = NP; p.scale = scale;
   ASB_DISPATCH_DTYPE(dtype, T, return launch<T>(p, num_tokens, stream));
   return 0;
+}
+
+extern "C" int asb_paged_attention(void* out, const void* q, const void* k_cache,
+                                   const void* v_cache, const int* block_tables,
+                                   const int* req_q_start, const int* req_pos_start,
+                                   float* part_m, float* part_l, float* part_acc,
+                                   int num_tokens, int R, int H, int KV, int hd, int bs,
+                                   int table_width, int window, int PS, int NP, float scale,
+                                   int dtype, cudaStream_t stream) {
+  return asb_paged_attention_sink(out, q, k_cache, v_cache, block_tables, req_q_start, req_pos_start, part_m, part_l,
+                                  part_acc, nullptr, num_tokens, R, H, KV, hd, bs, table_width, window, PS, NP, scale,
+                                  dtype, stream);
 }

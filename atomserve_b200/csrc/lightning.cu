@@ -21,6 +21,14 @@
 // leaving the state each segment starts from and the request's final state in its slot; mode 2
 // then adds decay^(t - first + 1) S_first^T q_t to every token of a segment. The sums are the
 // recurrence's, grouped differently: equal beyond rounding.
+//
+// The same kernel serves the other recurrences of this form (asb_linear_recurrence):
+//   - a decay and an input weight per token and head, S_t = a_t S_(t-1) + b_t k_t v_t^T, read from
+//     float32 arrays [T, H] (gated matrix memories; the arrays come from the gates' own scan);
+//   - a normaliser n_t = a_t n_(t-1) + b_t k_t kept beside S: it is the state's extra column
+//     V, whose value entry is 1, so n_t . q_t falls out as that column's output;
+//   - a rotation of q and k by position (pairs (i, i + rot / 2) of the first `rot` entries of a
+//     head, angle = position * inv_freq[i], float32) and a scale on each, applied as a tile is staged.
 #include "common.cuh"
 
 namespace {
@@ -40,13 +48,26 @@ struct LightningParams {
   int dp_shift, cpb_shift;  // log2 of the padded rows DS * RPT and of the value columns a block
   int zero_init;  // 1: the state starts at zero and is only written (a segment's local state)
   int carry;      // 1: add each token's share of the state it started from instead of running the recurrence
+  const float* tok_decay;   // [T, H] a decay per token, or null: decay[h]
+  const float* tok_gain;    // [T, H] a weight on each token's outer product, or null: 1
+  float* norm_state;        // [slots, H, D] the normaliser, or null: none is kept
+  float* norm_out;          // [T, H] n_t . q_t
+  const int* positions;     // [T], or null: no rotation
+  const float* inv_freq;    // [rot / 2]
+  int rot;
+  float q_scale, k_scale;
 };
 
 __device__ __forceinline__ float silu(float z) { return z / (1.f + expf(-z)); }
 
-template <typename T, int RPT>
+// GEN false: the fixed-decay form alone (per-token arrays, normaliser and rotation compiled out).
+template <typename T, int RPT, bool GEN>
 __global__ void __launch_bounds__(kThreads)
 lightning_kernel(const LightningParams p) {
+  const float* tok_decay = GEN ? p.tok_decay : nullptr;
+  const float* tok_gain = GEN ? p.tok_gain : nullptr;
+  float* norm_state = GEN ? p.norm_state : nullptr;
+  const int* positions = GEN ? p.positions : nullptr;
   asb::pdl_wait();
   asb::pdl_launch_dependents();
   extern __shared__ float smem[];
@@ -55,20 +76,24 @@ lightning_kernel(const LightningParams p) {
   float* qs = smem;                       // [TT][DP]
   float* ks = qs + kTokenTile * DP;       // [TT][DP]
   float* vs = ks + kTokenTile * DP;       // [TT][CPB]
+  __shared__ float decs[kTokenTile];
   const int r = blockIdx.x, h = blockIdx.y;
   const int ds = threadIdx.x & (DS - 1), cl = threadIdx.x >> (7 - p.cpb_shift);  // DS and 128 / DS are powers of two
   const int col = blockIdx.z * CPB + cl;
   const int row_lo = p.req_q_start[r], row_hi = p.req_q_start[r + 1];
   const int slot = p.state_slots[r];
-  const float dec = p.decay[h];
-  const bool live = col < p.V;
-  float* sp = p.state + (((size_t)slot * p.H + h) * p.D) * p.V + col;
+  const float dec = p.decay ? p.decay[h] : 1.f;
+  const bool ncol = norm_state != nullptr && col == p.V;  // this thread's column is the normaliser
+  const bool live = col < p.V || ncol;
+  float* sp = ncol ? norm_state + ((size_t)slot * p.H + h) * p.D : p.state + (((size_t)slot * p.H + h) * p.D) * p.V + col;
+  const size_t sstride = ncol ? 1 : p.V;
+  const int half = p.rot >> 1;
 
   float S[RPT];
 #pragma unroll
   for (int i = 0; i < RPT; ++i) {
     const int d = ds * RPT + i;
-    S[i] = (live && d < p.D && !p.zero_init) ? sp[(size_t)d * p.V] : 0.f;
+    S[i] = (live && d < p.D && !p.zero_init) ? sp[(size_t)d * sstride] : 0.f;
   }
   const T* proj = (const T*)p.proj;
   float weight = 1.f;
@@ -77,25 +102,40 @@ lightning_kernel(const LightningParams p) {
     __syncthreads();
     // the tile's loads are issued eight at a time before any is used
     constexpr int U = 8;
+    if (threadIdx.x < nt) decs[threadIdx.x] = tok_decay ? tok_decay[(size_t)(t0 + threadIdx.x) * p.H + h] : dec;
     for (int base = threadIdx.x; base < nt * DP; base += kThreads * U) {
-      float qv[U], kv[U];
+      float qv[U], kv[U], qp[U], kp[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int i = base + u * kThreads;
         const int t = i >> p.dp_shift, d = i - (t << p.dp_shift);
-        qv[u] = kv[u] = 0.f;
+        qv[u] = kv[u] = qp[u] = kp[u] = 0.f;
         if (i < nt * DP && d < p.D) {
           const T* row = proj + (size_t)(t0 + t) * p.stride + h * p.D + d;
           qv[u] = asb::to_float(row[p.q_off]);
           if (!p.carry) kv[u] = asb::to_float(row[p.k_off]);
+          if (positions && d < p.rot) {  // the other entry of this one's pair
+            const int other = d < half ? half : -half;
+            qp[u] = asb::to_float(row[p.q_off + other]);
+            if (!p.carry) kp[u] = asb::to_float(row[p.k_off + other]);
+          }
         }
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int i = base + u * kThreads;
         if (i < nt * DP) {
-          qs[i] = p.act ? silu(qv[u]) : qv[u];
-          ks[i] = p.act ? silu(kv[u]) : kv[u];
+          float qx = p.act ? silu(qv[u]) : qv[u], kx = p.act ? silu(kv[u]) : kv[u];
+          const int t = i >> p.dp_shift, d = i - (t << p.dp_shift);
+          if (positions && d < p.rot) {
+            float sn, cs;
+            sincosf((float)positions[t0 + t] * p.inv_freq[d < half ? d : d - half], &sn, &cs);
+            const float qo = p.act ? silu(qp[u]) : qp[u], ko = p.act ? silu(kp[u]) : kp[u];
+            qx = d < half ? qx * cs - qo * sn : qx * cs + qo * sn;
+            kx = d < half ? kx * cs - ko * sn : kx * cs + ko * sn;
+          }
+          qs[i] = GEN ? qx * p.q_scale : qx;
+          ks[i] = GEN ? kx * p.k_scale : kx;
         }
       }
     }
@@ -111,7 +151,12 @@ lightning_kernel(const LightningParams p) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const int i = base + u * kThreads;
-          if (i < nt * CPB) vs[i] = p.act ? silu(vv[u]) : vv[u];
+          if (i < nt * CPB) {
+            const int t = i >> p.cpb_shift, c = blockIdx.z * CPB + (i - (t << p.cpb_shift));
+            float v = p.act ? silu(vv[u]) : vv[u];
+            if (norm_state && c == p.V) v = 1.f;  // the normaliser's column
+            vs[i] = tok_gain ? v * tok_gain[(size_t)(t0 + t) * p.H + h] : v;
+          }
         }
       }
     }
@@ -131,13 +176,16 @@ lightning_kernel(const LightningParams p) {
         }
         float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
         for (int off = 1; off < DS; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-        weight *= dec;
-        if (ds == 0 && live) p.out[(size_t)(t0 + t) * p.H * p.V + h * p.V + col] += weight * o;
+        weight *= decs[t];
+        if (ds == 0 && live) {
+          if (ncol) p.norm_out[(size_t)(t0 + t) * p.H + h] += weight * o;
+          else p.out[(size_t)(t0 + t) * p.H * p.V + h * p.V + col] += weight * o;
+        }
       }
       continue;
     }
     for (int t = 0; t < nt; ++t) {
-      const float vv = vs[t * CPB + cl];
+      const float vv = vs[t * CPB + cl], dec = decs[t];
       const float4* kr = reinterpret_cast<const float4*>(ks + t * DP + ds * RPT);
       const float4* qr = reinterpret_cast<const float4*>(qs + t * DP + ds * RPT);
       float o4[4] = {0.f, 0.f, 0.f, 0.f};  // four chains instead of one of RPT dependent additions
@@ -155,14 +203,17 @@ lightning_kernel(const LightningParams p) {
       }
       float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
       for (int off = 1; off < DS; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-      if (ds == 0 && live) p.out[(size_t)(t0 + t) * p.H * p.V + h * p.V + col] = o;
+      if (ds == 0 && live) {
+        if (ncol) p.norm_out[(size_t)(t0 + t) * p.H + h] = o;
+        else p.out[(size_t)(t0 + t) * p.H * p.V + h * p.V + col] = o;
+      }
     }
   }
   if (p.carry) return;
 #pragma unroll
   for (int i = 0; i < RPT; ++i) {
     const int d = ds * RPT + i;
-    if (live && d < p.D) sp[(size_t)d * p.V] = S[i];
+    if (live && d < p.D) sp[(size_t)d * sstride] = S[i];
   }
 }
 
@@ -170,10 +221,11 @@ template <typename T, int RPT>
 int launch(const LightningParams& p, int R, cudaStream_t stream) {
   const int CPB = kThreads / p.DS;
   const size_t smem = sizeof(float) * kTokenTile * (2 * p.DS * RPT + CPB);
-  auto kern = lightning_kernel<T, RPT>;
+  const bool general = p.tok_decay || p.tok_gain || p.norm_state || p.positions || p.q_scale != 1.f || p.k_scale != 1.f;
+  auto kern = general ? lightning_kernel<T, RPT, true> : lightning_kernel<T, RPT, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return asb::fail("lightning_attention: shared memory %zu: %s", smem, cudaGetErrorString(e));
-  dim3 grid(R, p.H, (p.V + CPB - 1) / CPB);
+  dim3 grid(R, p.H, (p.V + (p.norm_state ? 1 : 0) + CPB - 1) / CPB);
   asb::launch(kern, grid, kThreads, smem, stream, p);
   return asb::check_launch("lightning_attention");
 }
@@ -183,11 +235,12 @@ int launch(const LightningParams& p, int R, cudaStream_t stream) {
 // segment starts from on exit; an element per thread, the segments of a request in order.
 __global__ void lightning_scan_kernel(float* __restrict__ local, float* __restrict__ state,
                                       const int* __restrict__ state_slots, const int* __restrict__ req_seg_start,
-                                      const int* __restrict__ seg_bounds, const float* __restrict__ decay, int H, int DV) {
+                                      const int* __restrict__ seg_bounds, const float* __restrict__ decay,
+                                      const float* __restrict__ tok_decay, int H, int DV) {
   asb::pdl_wait();
   asb::pdl_launch_dependents();
   const int r = blockIdx.x, h = blockIdx.y;
-  const float dec = decay[h], log_dec = logf(dec);
+  const float dec = decay ? decay[h] : 1.f, log_dec = logf(dec);
   float* sp = state + ((size_t)state_slots[r] * H + h) * DV;
   for (int e = blockIdx.z * blockDim.x + threadIdx.x; e < DV; e += gridDim.z * blockDim.x) {
     float S = sp[e];
@@ -202,8 +255,15 @@ __global__ void lightning_scan_kernel(float* __restrict__ local, float* __restri
         const int c = c0 + u;
         if (c >= c_end) break;
         local[((size_t)c * H + h) * DV + e] = S;
-        const float n = (float)(seg_bounds[c + 1] - seg_bounds[c]);
-        S = fmaf(dec == 1.f ? 1.f : expf(n * log_dec), S, own[u]);
+        float through;  // what is left of a state after the segment's tokens
+        if (tok_decay) {
+          through = 1.f;
+          for (int t = seg_bounds[c]; t < seg_bounds[c + 1]; ++t) through *= tok_decay[(size_t)t * H + h];
+        } else {
+          const float n = (float)(seg_bounds[c + 1] - seg_bounds[c]);
+          through = dec == 1.f ? 1.f : expf(n * log_dec);
+        }
+        S = fmaf(through, S, own[u]);
       }
     }
     sp[e] = S;
@@ -212,26 +272,45 @@ __global__ void lightning_scan_kernel(float* __restrict__ local, float* __restri
 
 }  // namespace
 
+// D * V elements per (request, head); for a normaliser, call it with its own buffers and V = 1.
+extern "C" int asb_recurrence_scan(float* local, float* state, const int* state_slots, const int* req_seg_start,
+                                   const int* seg_bounds, const float* decay, const float* tok_decay, int R, int H,
+                                   int D, int V, cudaStream_t stream) {
+  if (R == 0) return 0;
+  if (!decay && !tok_decay) return asb::fail("recurrence_scan: no decay given");
+  const int DV = D * V;
+  dim3 grid(R, H, (DV + 255) / 256 < 64 ? (DV + 255) / 256 : 64);
+  asb::launch(lightning_scan_kernel, grid, 256, 0, stream, local, state, state_slots, req_seg_start, seg_bounds, decay,
+              tok_decay, H, DV);
+  return asb::check_launch("recurrence_scan");
+}
+
 extern "C" int asb_lightning_scan(float* local, float* state, const int* state_slots, const int* req_seg_start,
                                   const int* seg_bounds, const float* decay, int R, int H, int D, int V,
                                   cudaStream_t stream) {
-  if (R == 0) return 0;
-  const int DV = D * V;
-  dim3 grid(R, H, (DV + 255) / 256 < 64 ? (DV + 255) / 256 : 64);
-  asb::launch(lightning_scan_kernel, grid, 256, 0, stream, local, state, state_slots, req_seg_start, seg_bounds, decay, H, DV);
-  return asb::check_launch("lightning_scan");
+  return asb_recurrence_scan(local, state, state_slots, req_seg_start, seg_bounds, decay, nullptr, R, H, D, V, stream);
 }
 
-extern "C" int asb_lightning_attention(float* out, const void* proj, int stride, int q_off, int k_off, int v_off,
-                                       float* state, const int* state_slots, const int* req_q_start,
-                                       const float* decay, int R, int H, int D, int V, int act, int mode, int dtype,
-                                       cudaStream_t stream) {
+// The general form. decay [H] or tok_decay [T, H] (one of them); tok_gain [T, H] or null;
+// norm_state [slots, H, D] with norm_out [T, H], or both null; positions [T] with inv_freq [rot / 2], or null.
+extern "C" int asb_linear_recurrence(float* out, const void* proj, int stride, int q_off, int k_off, int v_off,
+                                     float* state, const int* state_slots, const int* req_q_start,
+                                     const float* decay, const float* tok_decay, const float* tok_gain,
+                                     float* norm_state, float* norm_out, const int* positions, const float* inv_freq,
+                                     int rot, float q_scale, float k_scale, int R, int H, int D, int V, int act,
+                                     int mode, int dtype, cudaStream_t stream) {
   if (R == 0) return 0;
-  if (H < 1 || D < 1 || V < 1 || H > 65535) return asb::fail("lightning_attention: %d heads of %d x %d", H, D, V);
+  if (H < 1 || D < 1 || V < 1 || H > 65535) return asb::fail("linear_recurrence: %d heads of %d x %d", H, D, V);
+  if (!decay && !tok_decay) return asb::fail("linear_recurrence: no decay given");
+  if ((norm_state == nullptr) != (norm_out == nullptr)) return asb::fail("linear_recurrence: a normaliser needs its state and its output");
+  if (positions && (rot < 0 || rot % 2 || rot > D || !inv_freq)) return asb::fail("linear_recurrence: rotation of %d of %d entries", rot, D);
   LightningParams p;
   p.out = out; p.proj = proj; p.state = state; p.state_slots = state_slots; p.req_q_start = req_q_start;
   p.decay = decay; p.stride = stride; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off;
   p.H = H; p.D = D; p.V = V; p.act = act;
+  p.tok_decay = tok_decay; p.tok_gain = tok_gain; p.norm_state = norm_state; p.norm_out = norm_out;
+  p.positions = (positions && rot > 0) ? positions : nullptr; p.inv_freq = inv_freq; p.rot = rot;
+  p.q_scale = q_scale; p.k_scale = k_scale;
   p.zero_init = mode == 1;  // mode 0: the recurrence from the slots' states; 1: from zero, per segment; 2: the carried share
   p.carry = mode == 2;
   // rows of the state per thread: 64 from D = 64 on, fewer for narrow heads; D beyond 64 is
@@ -246,11 +325,20 @@ extern "C" int asb_lightning_attention(float* out, const void* proj, int stride,
   while ((1 << p.dp_shift) < ds * rpt) ++p.dp_shift;
   p.cpb_shift = 0;
   while ((1 << p.cpb_shift) < kThreads / ds) ++p.cpb_shift;
-  if ((V + kThreads / ds - 1) / (kThreads / ds) > 65535) return asb::fail("lightning_attention: value size %d", V);
+  if ((V + kThreads / ds) / (kThreads / ds) > 65535) return asb::fail("linear_recurrence: value size %d", V);
   ASB_DISPATCH_DTYPE(dtype, T, {
     if (rpt == 64) return launch<T, 64>(p, R, stream);
     if (rpt == 32) return launch<T, 32>(p, R, stream);
     return launch<T, 16>(p, R, stream);
   });
   return 0;
+}
+
+extern "C" int asb_lightning_attention(float* out, const void* proj, int stride, int q_off, int k_off, int v_off,
+                                       float* state, const int* state_slots, const int* req_q_start,
+                                       const float* decay, int R, int H, int D, int V, int act, int mode, int dtype,
+                                       cudaStream_t stream) {
+  return asb_linear_recurrence(out, proj, stride, q_off, k_off, v_off, state, state_slots, req_q_start, decay, nullptr,
+                               nullptr, nullptr, nullptr, nullptr, nullptr, 0, 1.f, 1.f, R, H, D, V, act, mode, dtype,
+                               stream);
 }

@@ -109,6 +109,7 @@ def paged_attention(
     partitions: tuple[int, int] | None = None,
     host_q_lens: list[int] | None = None,
     generic: bool = False,
+    sink: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """softmax(q k^T * scale) v for every new token, keys read in place from the pages.
 
@@ -116,6 +117,9 @@ def paged_attention(
     int32; req_q_start: [R + 1] int32 (rows of each request in q); req_pos_start: [R] int32.
     max_context: the largest position + 1 any request reaches in this step (host int).
     A query at position p sees keys j <= p of its request, and j > p - window with a window.
+
+    `sink` (float32 [H]): a logit per query head whose exponential joins the softmax's denominator
+    once; it has no key and no value and is not scaled. Only the general kernel knows it.
 
     bfloat16 with head size 64 or 128 runs the tensor-core kernels (decode kernel for requests
     that bring at most 8 tokens, prefill kernel for longer portions; `host_q_lens`, the tokens
@@ -134,6 +138,11 @@ def paged_attention(
             raise KernelLibraryError("paged_attention: index tensors must be contiguous int32")
     win = int(window) if window else 0
     out = torch.empty_like(q)
+    if sink is not None:
+        require_cuda(sink)
+        if sink.dtype != torch.float32 or sink.shape != (H,) or not sink.is_contiguous():
+            raise KernelLibraryError(f"paged_attention: sink must be contiguous float32 [{H}]")
+        generic = True
     if q.dtype == torch.bfloat16 and not generic and lib().asb_attention_mma_supported(hd, H // KV):
         return _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, req_pos_start,
                                     num_requests, max_context, win, scale, partitions, host_q_lens)  # fmt: skip
@@ -143,9 +152,9 @@ def paged_attention(
         part_m = torch.empty(T * H * np_, device=q.device, dtype=torch.float32)
         part_l = torch.empty_like(part_m)
         part_acc = torch.empty(T * H * np_ * hd, device=q.device, dtype=torch.float32)
-    check(lib().asb_paged_attention(
+    check(lib().asb_paged_attention_sink(
         ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start),
-        ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), T, num_requests, H, KV, hd, bs,
+        ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), ptr(sink), T, num_requests, H, KV, hd, bs,
         block_tables.shape[1], win, ps, np_, float(scale), dtype_code(q), stream()))  # fmt: skip
     return out
 

@@ -58,6 +58,16 @@ _SIGNATURES = {
     # linear attention with a decay per head
     "asb_lightning_attention": [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "asb_lightning_scan": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "asb_recurrence_scan": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "asb_linear_recurrence": [_P, _P, _I, _I, _I, _I] + [_P] * 10 + [_I, _F, _F] + [_I] * 7 + [_P],
+    # attention with a sink in the softmax's denominator
+    "asb_paged_attention_sink": [_P] * 11 + [_I] * 10 + [_F, _I, _P],
+    # blocks with the norm on the sublayer's output, and their mixers
+    "asb_residual_out_norm": [_P] * 10 + [_I, _I, _F, _F, _I, _I, _P],
+    "asb_head_norm_gate": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _I, _P],
+    "asb_projection_norm_store": [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    "asb_capped_gates_scan": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _F, _P],
+    "asb_gated_token_slice": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     # attention over a cached latent
     "asb_latent_prepare": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "asb_head_matmul": [_P, _I, _I, _I, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P],

@@ -1,4 +1,6 @@
-"""Linear attention with a decay per head over per-request state (csrc/lightning.cu)."""
+"""Linear attention over per-request state, S <- a S + b k v^T, o = S^T q: with a fixed decay per
+head ("lightning attention", retention) or a decay and an input weight per token (gated matrix
+memories), optionally with a normaliser and a rotation of q and k (csrc/lightning.cu)."""
 
 from __future__ import annotations
 
@@ -81,3 +83,62 @@ def lightning_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, 
                                             ptr(segments.index), ptr(segments.bounds), ptr(decay), segments.count, H, D, V,
                                             int(activation), mode, dtype_code(proj), stream()))  # fmt: skip
     return out
+
+
+def linear_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor,
+                      state_slots: torch.Tensor, req_q_start: torch.Tensor, num_requests: int, *,
+                      decay: torch.Tensor | None = None, token_decay: torch.Tensor | None = None,
+                      token_gain: torch.Tensor | None = None, norm_state: torch.Tensor | None = None,
+                      positions: torch.Tensor | None = None, inv_freq: torch.Tensor | None = None, rotary_dim: int = 0,
+                      q_scale: float = 1.0, k_scale: float = 1.0, activation: bool = False,
+                      segments: Segments | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:  # fmt: skip
+    """The general form of `lightning_attention`: S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = S_t^T q_t.
+
+    a: `decay` float32 [H], or `token_decay` float32 [T, H]; b: `token_gain` float32 [T, H], or 1.
+    `norm_state` float32 [slots, H, D]: a normaliser n_t = a_t n_(t-1) + b_t k_t is kept there too and
+    n_t . q_t returned as the second result, float32 [T, H]. `positions` int32 [T] with `inv_freq`
+    float32 [rotary_dim / 2]: q and k are rotated first, pairs (i, i + rotary_dim / 2) of each head's
+    first rotary_dim entries by position * inv_freq[i]. q_scale and k_scale multiply q and k after
+    that. Everything from the rotation on is float32. Returns (o float32 [T, H * V], n . q or None)."""
+    require_cuda(proj, state, state_slots, req_q_start, decay, token_decay, token_gain, norm_state, positions, inv_freq)
+    if proj.dim() != 2 or not proj.is_contiguous():
+        raise KernelLibraryError("linear_recurrence: proj must be a contiguous [tokens, columns] tensor")
+    if state.dtype != torch.float32 or state.dim() != 4 or not state.is_contiguous():
+        raise KernelLibraryError("linear_recurrence: state must be contiguous float32 [slots, H, D, V]")
+    T = proj.shape[0]
+    _, H, D, V = state.shape
+    if (decay is None) == (token_decay is None):
+        raise KernelLibraryError("linear_recurrence: give one of decay [H] and token_decay [T, H]")
+    for t, shape, name in ((decay, (H,), "decay"), (token_decay, (T, H), "token_decay"), (token_gain, (T, H), "token_gain"),
+                           (norm_state, (state.shape[0], H, D), "norm_state"), (inv_freq, (rotary_dim // 2,), "inv_freq")):  # fmt: skip
+        if t is not None and (t.dtype != torch.float32 or tuple(t.shape) != shape or not t.is_contiguous()):
+            raise KernelLibraryError(f"linear_recurrence: {name} must be contiguous float32 {list(shape)}")
+    for t in (state_slots, req_q_start, positions):
+        if t is not None and (t.dtype != torch.int32 or not t.is_contiguous()):
+            raise KernelLibraryError("linear_recurrence: index tensors must be contiguous int32")
+    if positions is not None and (rotary_dim % 2 or rotary_dim > D or inv_freq is None or positions.shape[0] < T):
+        raise KernelLibraryError(f"linear_recurrence: cannot rotate {rotary_dim} of {D} entries")
+    if max(q_off, k_off) + H * D > proj.shape[1] or v_off + H * V > proj.shape[1]:
+        raise KernelLibraryError("linear_recurrence: the column ranges lie outside proj")
+    out = torch.empty(T, H * V, device=proj.device, dtype=torch.float32)
+    nq = torch.empty(T, H, device=proj.device, dtype=torch.float32) if norm_state is not None else None
+    rot = rotary_dim if positions is not None else 0
+
+    def run(state_, slots_, starts_, norm_state_, count, mode):
+        check(lib().asb_linear_recurrence(ptr(out), ptr(proj), proj.shape[1], q_off, k_off, v_off, ptr(state_), ptr(slots_),
+                                          ptr(starts_), ptr(decay), ptr(token_decay), ptr(token_gain), ptr(norm_state_),
+                                          ptr(nq), ptr(positions), ptr(inv_freq), rot, float(q_scale), float(k_scale),
+                                          count, H, D, V, int(activation), mode, dtype_code(proj), stream()))  # fmt: skip
+
+    if segments is None:
+        run(state, state_slots, req_q_start, norm_state, num_requests, 0)
+        return out, nq
+    local = torch.empty(segments.count, H, D, V, device=proj.device, dtype=torch.float32)
+    local_n = torch.empty(segments.count, H, D, device=proj.device, dtype=torch.float32) if norm_state is not None else None
+    run(local, segments.index, segments.bounds, local_n, segments.count, 1)
+    for own, kept, v in ((local, state, V), (local_n, norm_state, 1)):
+        if own is not None:
+            check(lib().asb_recurrence_scan(ptr(own), ptr(kept), ptr(state_slots), ptr(segments.req_start), ptr(segments.bounds),
+                                            ptr(decay), ptr(token_decay), num_requests, H, D, v, stream()))  # fmt: skip
+    run(local, segments.index, segments.bounds, local_n, segments.count, 2)
+    return out, nq

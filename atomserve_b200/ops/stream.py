@@ -94,14 +94,25 @@ def gated_rms_norm(o: torch.Tensor, gate: torch.Tensor, gain: torch.Tensor, eps:
     return out
 
 
+ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "relu2": 2}
+
+
+def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
+    """Elementwise, float32 inside: "gelu" 0.5 z (1 + erf(z / sqrt 2)), "gelu_tanh" its tanh form,
+    "relu2" max(z, 0)^2."""
+    require_cuda(x)
+    if kind not in ACTIVATIONS:
+        raise KernelLibraryError(f"activation {kind!r} is not one of {sorted(ACTIVATIONS)}")
+    if not x.is_contiguous():
+        raise KernelLibraryError("activation takes a contiguous tensor")
+    out = torch.empty_like(x)
+    check(lib().asb_gelu(ptr(out), ptr(x), x.numel(), ACTIVATIONS[kind], dtype_code(x), stream()))
+    return out
+
+
 def gelu(x: torch.Tensor, tanh_form: bool = False) -> torch.Tensor:
     """The exact GELU 0.5 z (1 + erf(z / sqrt 2)), or its tanh form."""
-    require_cuda(x)
-    if not x.is_contiguous():
-        raise KernelLibraryError("gelu takes a contiguous tensor")
-    out = torch.empty_like(x)
-    check(lib().asb_gelu(ptr(out), ptr(x), x.numel(), int(tanh_form), dtype_code(x), stream()))
-    return out
+    return activation(x, "gelu_tanh" if tanh_form else "gelu")
 
 
 def clamped_glu(gate_up: torch.Tensor, limit: float, slope: float = 1.0, shift: float = 0.0) -> torch.Tensor:

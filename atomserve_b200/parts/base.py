@@ -212,6 +212,17 @@ class Mixer(Part):
         return out, then.forward(out)
 
 
+class TokenInput(Part):
+    """A sublayer fed by the step's token ids beside the stream: forward(x, h, ctx) -> (the new
+    float32 stream, its copy in the compute dtype), x the stream and h its compute-dtype copy."""
+
+    def bind_dtype(self, dtype: torch.dtype) -> None:
+        pass
+
+    def forward(self, x: torch.Tensor, h: torch.Tensor, ctx: StepContext) -> tuple[torch.Tensor, torch.Tensor]:
+        raise NotImplementedError
+
+
 class FeedForward(Part):
     def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
@@ -254,7 +265,7 @@ class Block(Part):
 # ---- registries ------------------------------------------------------------------------------
 
 _REGISTRIES: dict[str, dict[str, Callable[..., Any]]] = {
-    "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {}, "embedding": {}, "head": {},
+    "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {}, "embedding": {}, "head": {}, "token_input": {},
 }  # fmt: skip
 
 
@@ -286,4 +297,7 @@ def build_block(kind: str, mixer: Mixer, feed_forward: FeedForward, mixer_norm: 
 
 def _ensure_builtin() -> None:
     if "rms_norm" not in _REGISTRIES["norm"]:
-        from atomserve_b200.parts import attention, block, embedding, experts, latent_attention, lightning, mlp, norms, rotary  # noqa: F401
+        from atomserve_b200.parts import (  # noqa: F401
+            attention, block, embedding, experts, latent_attention, lightning, matrix_memory, mlp, norms, parallel, rotary,
+            sink_attention, token_input,
+        )

@@ -64,5 +64,43 @@ class PostNormBlock(Block):
         return x, h
 
 
+class OutputNormBlock(PostNormBlock):
+    """The arrangement with the norm on each sublayer's output, over a float32 residual stream:
+    x <- x + mult * norm1(mixer(x)); x <- x + mult * norm2(ff(x)), the sublayers reading x itself
+    (in the compute dtype); the norms are `OutputNorm`s and carry mult and the layer scales. A
+    layer without a feed-forward ends after its first half. A `token_input`, where the layer has
+    one (`attach`), adds what it makes of the step's token ids after that. A mixer that offers
+    `forward_halves` returns two outputs that the norm's kernel joins (two mixers side by side)."""
+
+    token_input = None
+
+    def attach(self, token_input) -> None:
+        self.token_input = token_input
+
+    def parts(self):
+        return super().parts() + ([self.token_input] if self.token_input is not None else [])
+
+    def bind_dtype(self, dtype: torch.dtype) -> None:
+        super().bind_dtype(dtype)
+        if self.token_input is not None:
+            self.token_input.bind_dtype(dtype)
+
+    def forward_chain(self, x: torch.Tensor, normed: torch.Tensor | None, ctx: StepContext, cache: CacheView | None,
+                      write_cache: bool, then: Norm | None) -> tuple[torch.Tensor, torch.Tensor | None]:  # fmt: skip
+        h = normed if normed is not None else ops.cast_rows(x, self.dtype)
+        halves = getattr(self.mixer, "forward_halves", None)
+        if halves is not None:
+            y, rest = halves(h, ctx, cache, write_cache)
+            x, h = self.mixer_norm.add_forward(x, y, rest)
+        else:
+            x, h = self.mixer_norm.add_forward(x, self.mixer.forward(h, None, ctx, cache, write_cache))
+        if self.has_feed_forward:
+            x, h = self.feed_forward_norm.add_forward(x, self.feed_forward.forward(h, None, ctx))
+        if self.token_input is not None:
+            x, h = self.token_input.forward(x, h, ctx)
+        return x, h
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "output_norm", OutputNormBlock)
 register_part("block", "post_norm", PostNormBlock)

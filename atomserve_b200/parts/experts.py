@@ -20,10 +20,15 @@ from atomserve_b200.parts.spec import TensorSpec
 
 
 class GeluMLP(FeedForward):
-    """down(gelu(up h)), the exact (erf) GELU or its tanh form; no biases."""
+    """down(act(up h)) with act the exact (erf) GELU, its tanh form, or (`activation="relu2"`) the
+    squared ReLU; no biases."""
 
-    def __init__(self, hidden_size: int, prefix: str, intermediate_size: int, tanh_form: bool = False):
+    def __init__(self, hidden_size: int, prefix: str, intermediate_size: int, tanh_form: bool = False,
+                 activation: str | None = None):  # fmt: skip
         self.hidden_size, self.prefix, self.intermediate_size, self.tanh_form = hidden_size, prefix, intermediate_size, tanh_form
+        self.activation = activation or ("gelu_tanh" if tanh_form else "gelu")
+        if self.activation not in ops.stream.ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r} is not one of {sorted(ops.stream.ACTIVATIONS)}")
         self.up = self.down = None
 
     def tensor_specs(self) -> list[TensorSpec]:
@@ -34,14 +39,14 @@ class GeluMLP(FeedForward):
         self.up, self.down = tensors[self.prefix + "up"], tensors[self.prefix + "down"]
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor | None, ctx: StepContext) -> torch.Tensor:
-        inner = ops.gelu(ops.linear(h, self.up), self.tanh_form)
+        inner = ops.activation(ops.linear(h, self.up), self.activation)
         # without a residual (a block that sums in float32 itself) the product stays float32
         return ops.linear(inner, self.down, residual, out_dtype=torch.float32 if residual is None else None)
 
     def forward_for_stream(self, h: torch.Tensor, ctx: StepContext):
         """ff(h) for a block that adds it to a float32 stream and norms the sum at once: float32, or
         the down projection's partial sums for that norm to add up (`ops.linear_for_stream`)."""
-        return ops.linear_for_stream(ops.gelu(ops.linear(h, self.up), self.tanh_form), self.down)
+        return ops.linear_for_stream(ops.activation(ops.linear(h, self.up), self.activation), self.down)
 
 
 class RoutedExperts(FeedForward):
@@ -120,5 +125,6 @@ class NoFeedForward(FeedForward):
 
 
 register_part("feed_forward", "gelu_mlp", GeluMLP)
+register_part("feed_forward", "activation_mlp", GeluMLP)
 register_part("feed_forward", "routed_experts", RoutedExperts)
 register_part("feed_forward", "none", NoFeedForward)

@@ -26,6 +26,11 @@ class DecoderModel:
             )
             for layer in spec.layers
         ]
+        for block, layer in zip(self.blocks, spec.layers):
+            if layer.token_input is not None:
+                if not hasattr(block, "attach"):
+                    raise ValueError(f"a {layer.block!r} block takes no token input")
+                block.attach(build_part("token_input", layer.token_input, d))
         self.schedule = spec.schedule
         for i, call in enumerate(self.schedule):
             if not 0 <= call.layer < len(self.blocks):

@@ -61,6 +61,43 @@ class StreamRMSNorm(RMSNorm):
         return ops.scaled_add_rms_norm(x, y, self.alpha, self.gain, self.eps, self.dtype)
 
 
+class OutputNorm(Norm):
+    """The norm of a block that norms each sublayer's output and adds it to a float32 stream:
+    `add_forward(x, y)` is x + mult * N(y) * gain * scale, returned as the new stream and in the
+    compute dtype. N is the centred norm (y - mean) / sqrt(var + eps), gain only, no bias, or with
+    `centred=False` the RMS norm; `scale_tensor` names a per-channel layer scale, if the layer has
+    one. `forward` is N(x) * gain of (rows of) the stream in the compute dtype, as a final norm."""
+
+    def __init__(self, hidden_size: int, prefix: str, eps: float, mult: float = 1.0, centred: bool = True,
+                 tensor: str | None = None, scale_tensor: str | None = None):  # fmt: skip
+        self.width, self.eps, self.mult, self.centred = hidden_size, float(eps), float(mult), bool(centred)
+        self.name, self.scale_name = tensor or prefix + "weight", scale_tensor
+        self.gain = self.scale = None
+        self.dtype = torch.float32
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        specs = [TensorSpec(self.name, (self.width,), kind="gain", init="gain")]
+        if self.scale_name:
+            specs.append(TensorSpec(self.scale_name, (self.width,), kind="gain", init="gain"))
+        return specs
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.gain = tensors[self.name]
+        self.scale = tensors[self.scale_name] if self.scale_name else None
+
+    def bind_dtype(self, dtype: torch.dtype) -> None:
+        self.dtype = dtype
+
+    def forward(self, x: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
+        return ops.residual_out_norm(None, x, self.gain, self.eps, self.dtype, centred=self.centred, rows=rows, want_stream=False)[1]
+
+    def add_forward(self, x: torch.Tensor, y: torch.Tensor, halves=None) -> tuple[torch.Tensor, torch.Tensor]:
+        """`halves=(b, gain_a, gain_b)`: the sublayer's output is (R(y) gain_a + R(b) gain_b) / 2 with
+        R the unit-RMS norm (two mixers side by side), formed in the same kernel."""
+        return ops.residual_out_norm(x, y, self.gain, self.eps, self.dtype, mult=self.mult, scale=self.scale,
+                                     centred=self.centred, halves=halves)  # fmt: skip
+
+
 class NoNorm(Norm):
     """The norm of a sublayer that a layer does not have."""
 
@@ -73,4 +110,5 @@ class NoNorm(Norm):
 
 register_part("norm", "rms_norm", RMSNorm)
 register_part("norm", "stream_rms_norm", StreamRMSNorm)
+register_part("norm", "output_norm", OutputNorm)
 register_part("norm", "none", NoNorm)

@@ -47,6 +47,9 @@ class LayerSpec:
     feed_forward: PartSpec
     mixer_norm: PartSpec
     feed_forward_norm: PartSpec
+    # a third sublayer fed by the step's token ids (kind in the "token_input" registry), for
+    # blocks that can `attach` one
+    token_input: PartSpec | None = None
 
 
 @dataclass(frozen=True)
