@@ -40,6 +40,7 @@ struct MmaParams {
   float* part_m;             // [T, H, NP]
   float* part_l;
   float* part_acc;           // [T, H, NP, HD]
+  const float* sink;         // [H] or null: a logit per head that joins the softmax's denominator once
   int T, R, H, KV, bs, table_width;
   int G, GC, HC;             // heads per kv head, heads per block (<= 16), chunks per kv head
   int QT;                    // prefill: tokens per 128-row tile
@@ -438,6 +439,16 @@ decode_attention_kernel(const MmaParams p) {
         den += ml[w * 16 + qr] * f;
         a += ma[(size_t)(w * 16 + qr) * HD + col] * f;
       }
+    if (p.sink && blockIdx.z == 0) {  // the sink counts once per row: in its first partition
+      const float sk = p.sink[head0 + qr];
+      if (den > 0.f) {
+        den += expf(sk - mx);  // (the sums stay relative to mx: nothing is rescaled)
+      } else {
+        mx = sk;
+        den = 1.f;
+        a = 0.f;
+      }
+    }
     const size_t orow = (size_t)row * p.H + head0 + qr;
     if (p.NP == 1) {
       p.out[orow * HD + col] = __float2bfloat16_rn(a / den);
@@ -645,6 +656,7 @@ prefill_attention_kernel(const MmaParams p) {
     if (rr >= num_rows) continue;
     const int qi = rr / gc, g = rr - qi * gc;
     __nv_bfloat16* o = p.out + ((size_t)(row0 + qi) * p.H + head0 + g) * HD;
+    if (p.sink) l[h] += exp2f(p.sink[head0 + g] * 1.4426950408889634f - m[h]);  // scores and maxima are in log2 units here
     const float inv = 1.f / l[h];
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i)
@@ -718,11 +730,11 @@ extern "C" int asb_attention_mma_supported(int hd, int group) {
 // short_rows > 0 (with run_decode alone): the number of rows of requests with at most 8 tokens in
 // a step that also holds longer portions; the decode kernel then starts blocks for those rows
 // only, and the scratch is [short_rows, H, NP(, hd)], merged by asb_attention_reduce_short.
-extern "C" int asb_paged_attention_mma(void* out, const void* q, const void* k_cache,
-                                       const void* v_cache, const int* block_tables,
-                                       const int* req_q_start, const int* req_pos_start,
-                                       float* part_m, float* part_l, float* part_acc,
-                                       int num_tokens, int R, int H, int KV, int hd, int bs,
+extern "C" int asb_paged_attention_mma_sink(void* out, const void* q, const void* k_cache,
+                                            const void* v_cache, const int* block_tables,
+                                            const int* req_q_start, const int* req_pos_start,
+                                            float* part_m, float* part_l, float* part_acc, const float* sink,
+                                            int num_tokens, int R, int H, int KV, int hd, int bs,
                                        int table_width, int window, int PS, int NP, float scale,
                                        int run_decode, int run_prefill, int all_single, int short_rows,
                                        cudaStream_t stream) {
@@ -739,7 +751,7 @@ extern "C" int asb_paged_attention_mma(void* out, const void* q, const void* k_c
   p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out;
   p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
   p.block_tables = block_tables; p.req_q_start = req_q_start; p.req_pos_start = req_pos_start;
-  p.part_m = part_m; p.part_l = part_l; p.part_acc = part_acc;
+  p.part_m = part_m; p.part_l = part_l; p.part_acc = part_acc; p.sink = sink;
   p.T = num_tokens; p.R = R; p.H = H; p.KV = KV; p.bs = bs; p.table_width = table_width;
   p.G = H / KV;
   p.GC = p.G < 16 ? p.G : 16;
@@ -749,4 +761,17 @@ extern "C" int asb_paged_attention_mma(void* out, const void* q, const void* k_c
   p.window = window; p.PS = PS; p.NP = NP; p.all_single = all_single; p.short_rows = short_rows; p.scale = scale;
   if (hd == 64) return launch_mma<64>(p, run_decode, run_prefill, stream);
   return launch_mma<128>(p, run_decode, run_prefill, stream);
+}
+
+extern "C" int asb_paged_attention_mma(void* out, const void* q, const void* k_cache,
+                                       const void* v_cache, const int* block_tables,
+                                       const int* req_q_start, const int* req_pos_start,
+                                       float* part_m, float* part_l, float* part_acc,
+                                       int num_tokens, int R, int H, int KV, int hd, int bs,
+                                       int table_width, int window, int PS, int NP, float scale,
+                                       int run_decode, int run_prefill, int all_single, int short_rows,
+                                       cudaStream_t stream) {
+  return asb_paged_attention_mma_sink(out, q, k_cache, v_cache, block_tables, req_q_start, req_pos_start, part_m, part_l,
+                                      part_acc, nullptr, num_tokens, R, H, KV, hd, bs, table_width, window, PS, NP, scale,
+                                      run_decode, run_prefill, all_single, short_rows, stream);
 }

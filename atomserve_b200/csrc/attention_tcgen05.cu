@@ -63,6 +63,7 @@ struct AttnParams {
   const int* req_q_start;    // [R + 1]
   const int* req_pos_start;  // [R]
   int* status;
+  const float* sink;         // [H] or null: a logit per head that joins the softmax's denominator once
   int T, R, H, KV, bs, table_width;
   int G, QT;                 // query heads per kv head, tokens per tile (128 / G)
   int window;
@@ -374,6 +375,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     }
     if (ok) {
       fence_after_sync();
+      // the sink: one more term of the sum, relative to the same maximum as the others (log2 units)
+      if (real && p.sink) l += exp2f(p.sink[head0 + (row - qi * p.G)] * 1.4426950408889634f - m);
       const float inv = real ? 1.f / l : 0.f;
       __nv_bfloat16* o = p.out + ((size_t)(row0 + qi) * p.H + head0 + (row - qi * p.G)) * HD;
 #pragma unroll 1
@@ -414,11 +417,11 @@ extern "C" int asb_attention_tcgen05_supported(int hd, int group, int block_size
 
 // Attention for every request that brings more than 8 tokens in this step (others are left
 // untouched for the decode kernel). q, out: [T, H, 128] bfloat16; caches [num_blocks, KV, bs, 128].
-extern "C" int asb_prefill_attention_tcgen05(void* out, const void* q, const void* k_cache, const void* v_cache,
-                                             const int* block_tables, const int* req_q_start,
-                                             const int* req_pos_start, int num_tokens, int R, int H, int KV,
-                                             int hd, int bs, int num_blocks, int table_width, int window,
-                                             float scale, int* status, cudaStream_t stream) {
+extern "C" int asb_prefill_attention_tcgen05_sink(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                                  const int* block_tables, const int* req_q_start,
+                                                  const int* req_pos_start, const float* sink, int num_tokens, int R,
+                                                  int H, int KV, int hd, int bs, int num_blocks, int table_width,
+                                                  int window, float scale, int* status, cudaStream_t stream) {
   if (num_tokens == 0 || R == 0) return 0;
   if (KV < 1 || H % KV) return asb::fail("prefill_attention_tcgen05: %d heads over %d kv heads", H, KV);
   if (!asb_attention_tcgen05_supported(hd, H / KV, bs))
@@ -428,6 +431,7 @@ extern "C" int asb_prefill_attention_tcgen05(void* out, const void* q, const voi
   p.out = (__nv_bfloat16*)out;
   p.block_tables = block_tables; p.req_q_start = req_q_start; p.req_pos_start = req_pos_start;
   p.status = status;
+  p.sink = sink;
   p.T = num_tokens; p.R = R; p.H = H; p.KV = KV; p.bs = bs; p.table_width = table_width;
   p.G = H / KV;
   p.QT = kRows / p.G;
@@ -455,4 +459,14 @@ extern "C" int asb_prefill_attention_tcgen05(void* out, const void* q, const voi
   if (blocks > 0x7fffffffLL) return asb::fail("prefill_attention_tcgen05: %lld blocks exceed the grid", blocks);
   asb::launch(kern, dim3((unsigned)blocks), kThreads, kSmem, stream, mq, mk, mv, p);
   return asb::check_launch("prefill_attention_tcgen05");
+}
+
+extern "C" int asb_prefill_attention_tcgen05(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                             const int* block_tables, const int* req_q_start,
+                                             const int* req_pos_start, int num_tokens, int R, int H, int KV,
+                                             int hd, int bs, int num_blocks, int table_width, int window,
+                                             float scale, int* status, cudaStream_t stream) {
+  return asb_prefill_attention_tcgen05_sink(out, q, k_cache, v_cache, block_tables, req_q_start, req_pos_start, nullptr,
+                                            num_tokens, R, H, KV, hd, bs, num_blocks, table_width, window, scale, status,
+                                            stream);
 }

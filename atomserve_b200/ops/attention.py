@@ -119,7 +119,7 @@ def paged_attention(
     A query at position p sees keys j <= p of its request, and j > p - window with a window.
 
     `sink` (float32 [H]): a logit per query head whose exponential joins the softmax's denominator
-    once; it has no key and no value and is not scaled. Only the general kernel knows it.
+    once; it has no key and no value and is not scaled.
 
     bfloat16 with head size 64 or 128 runs the tensor-core kernels (decode kernel for requests
     that bring at most 8 tokens, prefill kernel for longer portions; `host_q_lens`, the tokens
@@ -142,10 +142,9 @@ def paged_attention(
         require_cuda(sink)
         if sink.dtype != torch.float32 or sink.shape != (H,) or not sink.is_contiguous():
             raise KernelLibraryError(f"paged_attention: sink must be contiguous float32 [{H}]")
-        generic = True
     if q.dtype == torch.bfloat16 and not generic and lib().asb_attention_mma_supported(hd, H // KV):
         return _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, req_pos_start,
-                                    num_requests, max_context, win, scale, partitions, host_q_lens)  # fmt: skip
+                                    num_requests, max_context, win, scale, partitions, host_q_lens, sink)  # fmt: skip
     ps, np_ = partitions or plan_partitions(T, num_requests, KV, H // KV, max_context, win)
     part_m = part_l = part_acc = None
     if np_ > 1:
@@ -160,7 +159,7 @@ def paged_attention(
 
 
 def _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, req_pos_start, num_requests,
-                         max_context, win, scale, partitions, host_q_lens):  # fmt: skip
+                         max_context, win, scale, partitions, host_q_lens, sink=None):  # fmt: skip
     T, H, hd = q.shape
     KV, bs = k_cache.shape[1], k_cache.shape[2]
     if host_q_lens is None:
@@ -176,8 +175,8 @@ def _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, re
         from atomserve_b200.ops.linear import gemm_status
 
         def portions():
-            check(lib().asb_prefill_attention_tcgen05(
-                ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start), ptr(req_pos_start),
+            check(lib().asb_prefill_attention_tcgen05_sink(
+                ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start), ptr(req_pos_start), ptr(sink),
                 T, num_requests, H, KV, hd, bs, k_cache.shape[0], block_tables.shape[1], win, float(scale),
                 ptr(gemm_status(q.device)), stream()))  # fmt: skip
 
@@ -203,9 +202,9 @@ def _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, re
             part_acc = torch.empty(scratch_rows * H * np_ * hd, device=q.device, dtype=torch.float32)
 
         def single_tokens():
-            check(lib().asb_paged_attention_mma(
+            check(lib().asb_paged_attention_mma_sink(
                 ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start),
-                ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), T, num_requests, H, KV, hd, bs,
+                ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), ptr(sink), T, num_requests, H, KV, hd, bs,
                 block_tables.shape[1], win, ps, np_, float(scale), 1, 0, 0, compact, stream()))  # fmt: skip
             if np_ > 1 and compact:
                 check(lib().asb_attention_reduce_short(ptr(out), ptr(part_m), ptr(part_l), ptr(part_acc), ptr(req_q_start),
@@ -240,9 +239,9 @@ def _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, re
         part_m = torch.empty(T * H * np_, device=q.device, dtype=torch.float32)
         part_l = torch.empty_like(part_m)
         part_acc = torch.empty(T * H * np_ * hd, device=q.device, dtype=torch.float32)
-    check(lib().asb_paged_attention_mma(
+    check(lib().asb_paged_attention_mma_sink(
         ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start),
-        ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), T, num_requests, H, KV, hd, bs,
+        ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), ptr(sink), T, num_requests, H, KV, hd, bs,
         block_tables.shape[1], win, ps, np_, float(scale), int(has_short), int(has_long), int(all_single), 0,
         stream()))  # fmt: skip
     if np_ > 1:

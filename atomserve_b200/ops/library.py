@@ -62,6 +62,8 @@ _SIGNATURES = {
     "asb_linear_recurrence": [_P, _P, _I, _I, _I, _I] + [_P] * 10 + [_I, _F, _F] + [_I] * 7 + [_P],
     # attention with a sink in the softmax's denominator
     "asb_paged_attention_sink": [_P] * 11 + [_I] * 10 + [_F, _I, _P],
+    "asb_paged_attention_mma_sink": [_P] * 11 + [_I] * 10 + [_F, _I, _I, _I, _I, _P],
+    "asb_prefill_attention_tcgen05_sink": [_P] * 8 + [_I] * 9 + [_F, _P, _P],
     # blocks with the norm on the sublayer's output, and their mixers
     "asb_residual_out_norm": [_P] * 10 + [_I, _I, _F, _F, _I, _I, _P],
     "asb_head_norm_gate": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _I, _P],

@@ -528,10 +528,10 @@ def gefilix_shape(width: int, layers: int) -> dict:
                 embedding=dict(scale=1.0))
 
 
-def time_designs(widths: list[int], layers: int, steps: int, warmup: int, pk: dict) -> None:
-    """Prefill and decode of a Gefilix model and of a Qwen3 model of the same width and depth
-    (random weights), through the step function, and the design's own kernels one by one against
-    their rooflines beside the like kernels of Qwen3."""
+def design_timers(steps: int, warmup: int):
+    """(timed, model_times) for the design comparisons: `timed(fn, n)` is the mean milliseconds of n
+    calls after the warm-up, by CUDA events; `model_times(raw config, vocab)` the prefill of 2,048
+    tokens and the decode steps at batch 8 and 64 of a random model through the step function."""
     import torch
 
     from atomserve_b200 import ops
@@ -584,6 +584,23 @@ def time_designs(widths: list[int], layers: int, steps: int, warmup: int, pk: di
         torch.cuda.empty_cache()
         return out
 
+    return timed, model_times
+
+
+def time_designs(widths: list[int], layers: int, steps: int, warmup: int, pk: dict) -> None:
+    """Prefill and decode of a Gefilix model and of a Qwen3 model of the same width and depth
+    (random weights), through the step function, and the design's own kernels one by one against
+    their rooflines beside the like kernels of Qwen3."""
+    import torch
+
+    from atomserve_b200 import ops
+    from atomserve_b200.config import EngineConfig
+    from atomserve_b200.config.registry import config_from_dict
+    from atomserve_b200.engine.engine import create_engine
+    from atomserve_b200.engine.runner import Row
+    from atomserve_b200.weights import random_model
+
+    timed, model_times = design_timers(steps, warmup)
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")  # noqa: E731
     bw, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
     for width in widths:
@@ -656,6 +673,122 @@ def time_designs(widths: list[int], layers: int, steps: int, warmup: int, pk: di
         print(json.dumps(line), flush=True)
 
 
+# ---- the Zogepel design beside Gefilix at equal width (`--only zogepel`) --------------------------
+
+def zogepel_shape(width: int, layers: int) -> dict:
+    """Layer sizes that resemble a served model's: heads of 128; layers alternate a matrix memory
+    (keys half as wide as values) and attention in a window of 1,024 with four query heads a kv
+    head beside retention; a feed-forward of four times the width; token inputs of 128 a layer."""
+    heads = width // 128
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            mixer = dict(type="mlstm", mixer=dict(heads=heads, dim=64, vdim=128, gate_cap=15.0))
+        else:
+            left = dict(heads=heads, kv_heads=max(heads // 4, 1), dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=1024))
+            right = dict(heads=max(heads // 2, 1), dim=64, vdim=128, decay=[1.0 - 2.0 ** -(2 + h % 8) for h in range(max(heads // 2, 1))],
+                         rot=dict(base=10000.0, dims=64))
+            mixer = dict(type="parallel", mixer=dict(left=left, right=right))
+        out.append(dict(mixer, mlp=dict(kind="dense", ff=4 * width)))
+    return dict(architecture="Zogepel", vocab=32000, width=width, layers=out, norm=dict(eps=1e-6), residual_mult=0.7,
+                embedding=dict(scale=1.0), token_side=dict(dim=128))
+
+
+def time_zogepel(widths: list[int], layers: int, steps: int, warmup: int, pk: dict) -> None:
+    """Prefill and decode of a Zogepel model and of a Gefilix model of the same width and depth
+    (random weights), through the step function, and the design's own kernels one by one against
+    their rooflines beside the like kernels of Gefilix and Qwen3."""
+    import torch
+
+    from atomserve_b200 import ops
+
+    timed, model_times = design_timers(steps, warmup)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")  # noqa: E731
+    bw, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    bf = torch.bfloat16
+    for width in widths:
+        line = {"only": "zogepel", "width": width, "layers": layers, "peaks": pk["source"],
+                "zogepel": model_times(zogepel_shape(width, layers), 32000), "gefilix": model_times(gefilix_shape(width, layers), 32000)}
+        kern = {}
+        T, B, ctx, bs = PROMPT_TOKENS, 64, PROMPT_TOKENS, BLOCK_SIZE
+        H, D, V = width // 128, 64, 128
+        # the recurrences: one request of T tokens (in segments), and B requests of one token
+        proj = torch.randn(T, 2 * H * D + 2 * H * V, device="cuda", dtype=bf)
+        z = torch.randn(T, 2 * H, device="cuda")
+        zero = torch.zeros(H, device="cuda")
+        state, norm_state, top = torch.zeros(B, H, D, V, device="cuda"), torch.zeros(B, H, D, device="cuda"), torch.zeros(B, H, device="cuda")
+        decay = torch.full((H,), 0.99, device="cuda")
+        inv_freq = (1.0 / 10000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D)).cuda()
+        positions = i32(list(range(T)))
+        segments = ops.plan_segments([T], proj.device)
+        one, each = (i32([0]), i32([0, T])), (i32(list(range(B))), i32(list(range(B + 1))))
+
+        def memory(rows, slots, starts, n, seg):
+            a, b, _ = ops.capped_gates_scan(z[:rows], 0, H, H, zero, zero, 15.0, top, slots, starts, n)
+            return ops.linear_recurrence(proj[:rows], 0, H * D, 2 * H * D, state, slots, starts, n, token_decay=a, token_gain=b,
+                                         norm_state=norm_state, q_scale=D ** -0.5, segments=seg)  # fmt: skip
+
+        def retention(rows, slots, starts, n, seg):
+            return ops.linear_recurrence(proj[:rows], 0, H * D, 2 * H * D, state, slots, starts, n, decay=decay, k_scale=D ** -0.5,
+                                         positions=positions, inv_freq=inv_freq, rotary_dim=D, segments=seg)  # fmt: skip
+
+        def lightning(rows, slots, starts, n, seg):
+            return ops.lightning_attention(proj[:rows], 0, H * D, 2 * H * D, state, slots, starts, decay, n, segments=seg)
+
+        for name, fn, cols in (("matrix_memory", memory, V + 1), ("retention", retention, V), ("lightning", lightning, V)):
+            ms = timed(lambda: fn(T, *one, 1, segments), 8)
+            kern[f"{name}_prefill"] = {"ms": round(ms, 4), "gflops": round(4.0 * T * H * D * cols / ms / 1e6, 1), "note": "float32 CUDA cores"}
+            ms = timed(lambda: fn(B, *each, B, None))
+            kern[f"{name}_decode_b64"] = {"ms": round(ms, 4), "hbm_frac": round(2.0 * B * H * D * cols * 4 / (ms * 1e-3) / bw, 3)}
+        # attention in a window of 1,024 with a sink (the general kernel) beside the same window without (the tensor-core kernels)
+        KV, hd, window = max(H // 4, 1), 128, 1024
+        pages_per = ctx // bs
+        tables = i32([[r * pages_per + j for j in range(pages_per)] for r in range(B)])
+        k_pages = torch.randn(B * pages_per, KV, bs, hd, device="cuda", dtype=bf)
+        v_pages = torch.randn_like(k_pages)
+        sink = torch.zeros(H, device="cuda")
+        q = torch.randn(B, H, hd, device="cuda", dtype=bf)
+        starts, at = i32(list(range(B + 1))), i32([ctx - 1] * B)
+        for name, sk in (("sink_attention", sink), ("paged_attention", None)):
+            ms = timed(lambda: ops.paged_attention(q, k_pages, v_pages, tables, starts, at, num_requests=B, max_context=ctx, window=window,
+                                                   scale=0.088, host_q_lens=[1] * B, sink=sk))  # fmt: skip
+            kern[f"{name}_decode_b64"] = {"ms": round(ms, 4), "hbm_frac": round(2.0 * B * window * KV * hd * 2 / (ms * 1e-3) / bw, 3)}
+        qp = torch.randn(T, H, hd, device="cuda", dtype=bf)
+        t1 = i32([list(range(pages_per))])
+        seen = sum(min(t + 1, window) for t in range(T))
+        for name, sk in (("sink_attention", sink), ("paged_attention", None)):
+            ms = timed(lambda: ops.paged_attention(qp, k_pages, v_pages, t1, i32([0, T]), i32([0]), num_requests=1, max_context=T,
+                                                   window=window, scale=0.088, host_q_lens=[T], sink=sk), 4)  # fmt: skip
+            kern[f"{name}_prefill"] = {"ms": round(ms, 3), "tc_frac": round(4.0 * seen * H * hd / (ms * 1e-3) / tf, 4)}
+        # the norms and gates around the sublayers, T rows: bytes moved over the measured copy bandwidth
+        x, y = torch.randn(T, width, device="cuda"), torch.randn(T, width, device="cuda")
+        gain = torch.ones(width, device="cuda")
+        ms = timed(lambda: ops.residual_out_norm(x, y, gain, 1e-6, bf, mult=0.7, scale=gain))
+        kern["residual_out_norm"] = {"ms": round(ms, 4), "hbm_frac": round(T * width * 14 / (ms * 1e-3) / bw, 3)}
+        ms = timed(lambda: ops.residual_out_norm(x, y, gain, 1e-6, bf, mult=0.7, scale=gain, halves=(y, gain, gain)))
+        kern["residual_out_norm_two_halves"] = {"ms": round(ms, 4), "hbm_frac": round(T * width * 18 / (ms * 1e-3) / bw, 3)}
+        ms = timed(lambda: ops.scaled_add_rms_norm(x, y, 1.0, gain, 1e-6, bf))
+        kern["scaled_add_rms_norm"] = {"ms": round(ms, 4), "hbm_frac": round(T * width * 14 / (ms * 1e-3) / bw, 3)}
+        o = torch.randn(T, H * V, device="cuda")
+        gate = torch.randn(T, H * V, device="cuda", dtype=bf)
+        g2 = torch.ones(H * V, device="cuda")
+        ms = timed(lambda: ops.head_norm_gate(o, gate, H, gain=g2, eps=1e-6))
+        kern["head_norm_gate"] = {"ms": round(ms, 4), "hbm_frac": round(T * H * V * 8 / (ms * 1e-3) / bw, 3)}
+        ms = timed(lambda: ops.gated_rms_norm(o, gate, g2, 1e-6))
+        kern["gated_rms_norm"] = {"ms": round(ms, 4), "hbm_frac": round(T * H * V * 8 / (ms * 1e-3) / bw, 3)}
+        qk = torch.randn(T, (H + 2 * KV) * hd, device="cuda", dtype=bf)
+        slots = i32(list(range(T)))
+        gq, gk = torch.ones(H * hd, device="cuda"), torch.ones(KV * hd, device="cuda")
+        ms = timed(lambda: ops.projection_norm_store(qk, 0, H * hd, H, KV, hd, gq, gk, 1e-6, slots, k_pages, v_pages))
+        kern["projection_norm_store"] = {"ms": round(ms, 4), "hbm_frac": round(T * (2 * H + 3 * KV) * hd * 2 / (ms * 1e-3) / bw, 3)}
+        g1 = torch.ones(hd, device="cuda")
+        ms = timed(lambda: ops.qk_norm_rope_store(qk, H, KV, hd, positions, q_gain=g1, k_gain=g1, eps=1e-6, inv_freq=inv_freq.repeat(2)[: hd // 2],
+                                                  rotary_dim=hd, slots=slots, k_cache=k_pages, v_cache=v_pages))  # fmt: skip
+        kern["qk_norm_rope_store"] = {"ms": round(ms, 4), "hbm_frac": round(T * (2 * H + 4 * KV) * hd * 2 / (ms * 1e-3) / bw, 3)}
+        line["kernels"] = kern
+        print(json.dumps(line), flush=True)
+
+
 def reference_arm(args) -> int:
     """The same measurement on the unmodified reference (baseline/reference_arm.py): its own
     engine, sampler and PyTorch model code on this GPU, nothing of this package."""
@@ -711,7 +844,7 @@ def main() -> int:
                         help="fewer layers than the model has (same layer sizes), where time or memory needs it")  # fmt: skip
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--only", choices=["decode", "prefill", "gemm", "serve", "attention", "sampling", "designs"], help="time just this (for profiling small cases and the other shapes)")
+    parser.add_argument("--only", choices=["decode", "prefill", "gemm", "serve", "attention", "sampling", "designs", "zogepel"], help="time just this (for profiling small cases and the other shapes)")
     parser.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="with --only decode/prefill/serve: layer sizes of Qwen3-8B, -14B or -32B")
     parser.add_argument("--context", type=int, default=PROMPT_TOKENS, help="with --only decode: tokens each request holds when decoding starts")
     parser.add_argument("--requests", type=int, default=32, help="with --only serve: requests submitted at once")
@@ -719,7 +852,7 @@ def main() -> int:
     parser.add_argument("--budget", type=int, default=512, help="with --only serve: the scheduler's token budget per step")
     parser.add_argument("--gemm-shape", default="all", help="with --only gemm: qkv, o, gate_up, down, lm_head or all")
     parser.add_argument("--gemm-tokens", default="1,8,64,2048", help="with --only gemm: token counts, comma-separated")
-    parser.add_argument("--widths", default="2048,4096", help="with --only designs: model widths, comma-separated")
+    parser.add_argument("--widths", default="2048,4096", help="with --only designs or zogepel: model widths, comma-separated")
     parser.add_argument("--timeline", action="store_true", help="with --only gemm: where a decode-size call's time goes")
     args = parser.parse_args()
     args.layers_given = any(a == "--layers" or a.startswith("--layers=") for a in sys.argv[1:])
@@ -744,6 +877,9 @@ def main() -> int:
         return 0
     if args.only == "designs":
         time_designs([int(w) for w in args.widths.split(",")], args.layers if args.layers_given else 4, max(args.steps // 4, 8), warmup, pk)
+        return 0
+    if args.only == "zogepel":
+        time_zogepel([int(w) for w in args.widths.split(",")], args.layers if args.layers_given else 4, max(args.steps // 4, 8), warmup, pk)
         return 0
     if args.only == "gemm" and args.timeline:
         gemm_timelines(args.gemm_shape, [int(t) for t in args.gemm_tokens.split(",")])
