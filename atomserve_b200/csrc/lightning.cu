@@ -25,10 +25,13 @@
 // The same kernel serves the other recurrences of this form (asb_linear_recurrence):
 //   - a decay and an input weight per token and head, S_t = a_t S_(t-1) + b_t k_t v_t^T, read from
 //     float32 arrays [T, H] (gated matrix memories; the arrays come from the gates' own scan);
-//   - a normaliser n_t = a_t n_(t-1) + b_t k_t kept beside S: it is the state's extra column
-//     V, whose value entry is 1, so n_t . q_t falls out as that column's output;
+//   - a normaliser n_t = a_t n_(t-1) + b_t k_t kept beside S and n_t . q_t given out with o_t: the
+//     first warp of a (request, head)'s first block walks it through shared memory ahead of its
+//     share of S (a few multiply-adds a token);
 //   - a rotation of q and k by position (pairs (i, i + rot / 2) of the first `rot` entries of a
-//     head, angle = position * inv_freq[i], float32) and a scale on each, applied as a tile is staged.
+//     head; the cosines and sines come from a table [T, rot / 2] made once per step by
+//     asb_rotary_table, float32 `sincosf` of position * inv_freq[i]) and a scale on each, applied as
+//     a tile is staged.
 #include "common.cuh"
 
 namespace {
@@ -52,8 +55,7 @@ struct LightningParams {
   const float* tok_gain;    // [T, H] a weight on each token's outer product, or null: 1
   float* norm_state;        // [slots, H, D] the normaliser, or null: none is kept
   float* norm_out;          // [T, H] n_t . q_t
-  const int* positions;     // [T], or null: no rotation
-  const float* inv_freq;    // [rot / 2]
+  const float2* rot_table;  // [T, rot / 2] (cos, sin) of each token's angles, or null: no rotation
   int rot;
   float q_scale, k_scale;
 };
@@ -67,7 +69,7 @@ lightning_kernel(const LightningParams p) {
   const float* tok_decay = GEN ? p.tok_decay : nullptr;
   const float* tok_gain = GEN ? p.tok_gain : nullptr;
   float* norm_state = GEN ? p.norm_state : nullptr;
-  const int* positions = GEN ? p.positions : nullptr;
+  const float2* rot_table = GEN ? p.rot_table : nullptr;
   asb::pdl_wait();
   asb::pdl_launch_dependents();
   extern __shared__ float smem[];
@@ -76,17 +78,22 @@ lightning_kernel(const LightningParams p) {
   float* qs = smem;                       // [TT][DP]
   float* ks = qs + kTokenTile * DP;       // [TT][DP]
   float* vs = ks + kTokenTile * DP;       // [TT][CPB]
-  __shared__ float decs[kTokenTile];
+  __shared__ float decs[kTokenTile], gains[kTokenTile];
+  float* ns = vs + kTokenTile * CPB;      // [DP] the normaliser (general form, first block of a head)
   const int r = blockIdx.x, h = blockIdx.y;
   const int ds = threadIdx.x & (DS - 1), cl = threadIdx.x >> (7 - p.cpb_shift);  // DS and 128 / DS are powers of two
   const int col = blockIdx.z * CPB + cl;
   const int row_lo = p.req_q_start[r], row_hi = p.req_q_start[r + 1];
   const int slot = p.state_slots[r];
   const float dec = p.decay ? p.decay[h] : 1.f;
-  const bool ncol = norm_state != nullptr && col == p.V;  // this thread's column is the normaliser
-  const bool live = col < p.V || ncol;
-  float* sp = ncol ? norm_state + ((size_t)slot * p.H + h) * p.D : p.state + (((size_t)slot * p.H + h) * p.D) * p.V + col;
-  const size_t sstride = ncol ? 1 : p.V;
+  const bool live = col < p.V;
+  float* sp = p.state + (((size_t)slot * p.H + h) * p.D) * p.V + col;
+  const size_t sstride = p.V;
+  // the normaliser is the first warp's of the head's first block
+  const bool keeps_norm = GEN && norm_state != nullptr && blockIdx.z == 0 && threadIdx.x < 32;
+  float* np_ = norm_state ? norm_state + ((size_t)slot * p.H + h) * p.D : nullptr;
+  if (keeps_norm)
+    for (int d = threadIdx.x; d < p.D; d += 32) ns[d] = p.zero_init ? 0.f : np_[d];
   const int half = p.rot >> 1;
 
   float S[RPT];
@@ -102,7 +109,10 @@ lightning_kernel(const LightningParams p) {
     __syncthreads();
     // the tile's loads are issued eight at a time before any is used
     constexpr int U = 8;
-    if (threadIdx.x < nt) decs[threadIdx.x] = tok_decay ? tok_decay[(size_t)(t0 + threadIdx.x) * p.H + h] : dec;
+    if (threadIdx.x < nt) {
+      decs[threadIdx.x] = tok_decay ? tok_decay[(size_t)(t0 + threadIdx.x) * p.H + h] : dec;
+      gains[threadIdx.x] = tok_gain ? tok_gain[(size_t)(t0 + threadIdx.x) * p.H + h] : 1.f;
+    }
     for (int base = threadIdx.x; base < nt * DP; base += kThreads * U) {
       float qv[U], kv[U], qp[U], kp[U];
 #pragma unroll
@@ -114,7 +124,7 @@ lightning_kernel(const LightningParams p) {
           const T* row = proj + (size_t)(t0 + t) * p.stride + h * p.D + d;
           qv[u] = asb::to_float(row[p.q_off]);
           if (!p.carry) kv[u] = asb::to_float(row[p.k_off]);
-          if (positions && d < p.rot) {  // the other entry of this one's pair
+          if (rot_table && d < p.rot) {  // the other entry of this one's pair
             const int other = d < half ? half : -half;
             qp[u] = asb::to_float(row[p.q_off + other]);
             if (!p.carry) kp[u] = asb::to_float(row[p.k_off + other]);
@@ -127,9 +137,9 @@ lightning_kernel(const LightningParams p) {
         if (i < nt * DP) {
           float qx = p.act ? silu(qv[u]) : qv[u], kx = p.act ? silu(kv[u]) : kv[u];
           const int t = i >> p.dp_shift, d = i - (t << p.dp_shift);
-          if (positions && d < p.rot) {
-            float sn, cs;
-            sincosf((float)positions[t0 + t] * p.inv_freq[d < half ? d : d - half], &sn, &cs);
+          if (rot_table && d < p.rot) {
+            const float2 turn = rot_table[(size_t)(t0 + t) * half + (d < half ? d : d - half)];
+            const float cs = turn.x, sn = turn.y;
             const float qo = p.act ? silu(qp[u]) : qp[u], ko = p.act ? silu(kp[u]) : kp[u];
             qx = d < half ? qx * cs - qo * sn : qx * cs + qo * sn;
             kx = d < half ? kx * cs - ko * sn : kx * cs + ko * sn;
@@ -152,15 +162,34 @@ lightning_kernel(const LightningParams p) {
         for (int u = 0; u < U; ++u) {
           const int i = base + u * kThreads;
           if (i < nt * CPB) {
-            const int t = i >> p.cpb_shift, c = blockIdx.z * CPB + (i - (t << p.cpb_shift));
-            float v = p.act ? silu(vv[u]) : vv[u];
-            if (norm_state && c == p.V) v = 1.f;  // the normaliser's column
-            vs[i] = tok_gain ? v * tok_gain[(size_t)(t0 + t) * p.H + h] : v;
+            const float v = p.act ? silu(vv[u]) : vv[u];
+            vs[i] = tok_gain ? v * tok_gain[(size_t)(t0 + (i >> p.cpb_shift)) * p.H + h] : v;
           }
         }
       }
     }
     __syncthreads();
+    if (keeps_norm) {
+      // n_t = a_t n_(t-1) + b_t k_t and n_t . q_t, or in the carried pass the share of the n this segment started from
+      float w = weight;
+      for (int t = 0; t < nt; ++t) {
+        float part = 0.f;
+        for (int d = threadIdx.x; d < p.D; d += 32) {
+          float n = ns[d];
+          if (!p.carry) {
+            n = fmaf(decs[t], n, gains[t] * ks[t * DP + d]);
+            ns[d] = n;
+          }
+          part = fmaf(n, qs[t * DP + d], part);
+        }
+        part = asb::warp_sum(part);
+        w *= decs[t];
+        if (threadIdx.x == 0) {
+          if (p.carry) p.norm_out[(size_t)(t0 + t) * p.H + h] += w * part;
+          else p.norm_out[(size_t)(t0 + t) * p.H + h] = part;
+        }
+      }
+    }
     if (p.carry) {
       // o_t += decay^(t - first + 1) * S_first^T q_t: what the tokens before this segment contribute
       for (int t = 0; t < nt; ++t) {
@@ -177,10 +206,7 @@ lightning_kernel(const LightningParams p) {
         float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
         for (int off = 1; off < DS; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
         weight *= decs[t];
-        if (ds == 0 && live) {
-          if (ncol) p.norm_out[(size_t)(t0 + t) * p.H + h] += weight * o;
-          else p.out[(size_t)(t0 + t) * p.H * p.V + h * p.V + col] += weight * o;
-        }
+        if (ds == 0 && live) p.out[(size_t)(t0 + t) * p.H * p.V + h * p.V + col] += weight * o;
       }
       continue;
     }
@@ -203,13 +229,12 @@ lightning_kernel(const LightningParams p) {
       }
       float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
       for (int off = 1; off < DS; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-      if (ds == 0 && live) {
-        if (ncol) p.norm_out[(size_t)(t0 + t) * p.H + h] = o;
-        else p.out[(size_t)(t0 + t) * p.H * p.V + h * p.V + col] = o;
-      }
+      if (ds == 0 && live) p.out[(size_t)(t0 + t) * p.H * p.V + h * p.V + col] = o;
     }
   }
   if (p.carry) return;
+  if (keeps_norm)
+    for (int d = threadIdx.x; d < p.D; d += 32) np_[d] = ns[d];
 #pragma unroll
   for (int i = 0; i < RPT; ++i) {
     const int d = ds * RPT + i;
@@ -220,12 +245,12 @@ lightning_kernel(const LightningParams p) {
 template <typename T, int RPT>
 int launch(const LightningParams& p, int R, cudaStream_t stream) {
   const int CPB = kThreads / p.DS;
-  const size_t smem = sizeof(float) * kTokenTile * (2 * p.DS * RPT + CPB);
-  const bool general = p.tok_decay || p.tok_gain || p.norm_state || p.positions || p.q_scale != 1.f || p.k_scale != 1.f;
+  const size_t smem = sizeof(float) * (kTokenTile * (2 * p.DS * RPT + CPB) + p.DS * RPT);
+  const bool general = p.tok_decay || p.tok_gain || p.norm_state || p.rot_table || p.q_scale != 1.f || p.k_scale != 1.f;
   auto kern = general ? lightning_kernel<T, RPT, true> : lightning_kernel<T, RPT, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return asb::fail("lightning_attention: shared memory %zu: %s", smem, cudaGetErrorString(e));
-  dim3 grid(R, p.H, (p.V + (p.norm_state ? 1 : 0) + CPB - 1) / CPB);
+  dim3 grid(R, p.H, (p.V + CPB - 1) / CPB);
   asb::launch(kern, grid, kThreads, smem, stream, p);
   return asb::check_launch("lightning_attention");
 }
@@ -270,7 +295,30 @@ __global__ void lightning_scan_kernel(float* __restrict__ local, float* __restri
   }
 }
 
+// (cos, sin) of position * inv_freq[i] for every token of a step, float32: once per step for all
+// the layers that rotate by the same frequencies.
+__global__ void rotary_table_kernel(float2* __restrict__ table, const int* __restrict__ positions,
+                                    const float* __restrict__ inv_freq, int half, long long total) {
+  asb::pdl_wait();
+  asb::pdl_launch_dependents();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    float sn, cs;
+    sincosf((float)positions[i / half] * inv_freq[i % half], &sn, &cs);
+    table[i] = make_float2(cs, sn);
+  }
+}
+
 }  // namespace
+
+extern "C" int asb_rotary_table(float* table, const int* positions, const float* inv_freq, int num_tokens, int half,
+                                cudaStream_t stream) {
+  if (num_tokens == 0 || half == 0) return 0;
+  const long long total = (long long)num_tokens * half;
+  const long long blocks = (total + 255) / 256;
+  asb::launch(rotary_table_kernel, (unsigned)(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, stream,
+              reinterpret_cast<float2*>(table), positions, inv_freq, half, total);
+  return asb::check_launch("rotary_table");
+}
 
 // D * V elements per (request, head); for a normaliser, call it with its own buffers and V = 1.
 extern "C" int asb_recurrence_scan(float* local, float* state, const int* state_slots, const int* req_seg_start,
@@ -292,24 +340,24 @@ extern "C" int asb_lightning_scan(float* local, float* state, const int* state_s
 }
 
 // The general form. decay [H] or tok_decay [T, H] (one of them); tok_gain [T, H] or null;
-// norm_state [slots, H, D] with norm_out [T, H], or both null; positions [T] with inv_freq [rot / 2], or null.
+// norm_state [slots, H, D] with norm_out [T, H], or both null; rot_table [T, rot / 2, 2] (asb_rotary_table), or null.
 extern "C" int asb_linear_recurrence(float* out, const void* proj, int stride, int q_off, int k_off, int v_off,
                                      float* state, const int* state_slots, const int* req_q_start,
                                      const float* decay, const float* tok_decay, const float* tok_gain,
-                                     float* norm_state, float* norm_out, const int* positions, const float* inv_freq,
+                                     float* norm_state, float* norm_out, const float* rot_table,
                                      int rot, float q_scale, float k_scale, int R, int H, int D, int V, int act,
                                      int mode, int dtype, cudaStream_t stream) {
   if (R == 0) return 0;
   if (H < 1 || D < 1 || V < 1 || H > 65535) return asb::fail("linear_recurrence: %d heads of %d x %d", H, D, V);
   if (!decay && !tok_decay) return asb::fail("linear_recurrence: no decay given");
   if ((norm_state == nullptr) != (norm_out == nullptr)) return asb::fail("linear_recurrence: a normaliser needs its state and its output");
-  if (positions && (rot < 0 || rot % 2 || rot > D || !inv_freq)) return asb::fail("linear_recurrence: rotation of %d of %d entries", rot, D);
+  if (rot_table && (rot < 0 || rot % 2 || rot > D)) return asb::fail("linear_recurrence: rotation of %d of %d entries", rot, D);
   LightningParams p;
   p.out = out; p.proj = proj; p.state = state; p.state_slots = state_slots; p.req_q_start = req_q_start;
   p.decay = decay; p.stride = stride; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off;
   p.H = H; p.D = D; p.V = V; p.act = act;
   p.tok_decay = tok_decay; p.tok_gain = tok_gain; p.norm_state = norm_state; p.norm_out = norm_out;
-  p.positions = (positions && rot > 0) ? positions : nullptr; p.inv_freq = inv_freq; p.rot = rot;
+  p.rot_table = (rot_table && rot > 0) ? reinterpret_cast<const float2*>(rot_table) : nullptr; p.rot = rot;
   p.q_scale = q_scale; p.k_scale = k_scale;
   p.zero_init = mode == 1;  // mode 0: the recurrence from the slots' states; 1: from zero, per segment; 2: the carried share
   p.carry = mode == 2;
@@ -339,6 +387,5 @@ extern "C" int asb_lightning_attention(float* out, const void* proj, int stride,
                                        const float* decay, int R, int H, int D, int V, int act, int mode, int dtype,
                                        cudaStream_t stream) {
   return asb_linear_recurrence(out, proj, stride, q_off, k_off, v_off, state, state_slots, req_q_start, decay, nullptr,
-                               nullptr, nullptr, nullptr, nullptr, nullptr, 0, 1.f, 1.f, R, H, D, V, act, mode, dtype,
-                               stream);
+                               nullptr, nullptr, nullptr, nullptr, 0, 1.f, 1.f, R, H, D, V, act, mode, dtype, stream);
 }

@@ -412,6 +412,9 @@ class ModelRunner:
             if self._graph_pool is None:
                 # one memory pool for all graphs: only one of them runs at a time
                 self._graph_pool = torch.cuda.graph_pool_handle()
+            # what the parts worked out for the step in the warm-up run (device tables among it) is made
+            # again inside the capture, so that the graph holds the kernels that make it
+            ctx.plans.clear()
             before = launches()
             with torch.cuda.graph(graph, pool=self._graph_pool):
                 self.model.forward(ctx, self.views, logits)

@@ -85,21 +85,33 @@ def lightning_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, 
     return out
 
 
+def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """(cos, sin) of position * inv_freq[i] for every token, float32 [T, len(inv_freq), 2]: made once
+    per step for all the layers that rotate by the same frequencies."""
+    require_cuda(positions, inv_freq)
+    if positions.dtype != torch.int32 or inv_freq.dtype != torch.float32 or not positions.is_contiguous() or not inv_freq.is_contiguous():
+        raise KernelLibraryError("rotary_table takes contiguous int32 positions and float32 frequencies")
+    table = torch.empty(positions.shape[0], inv_freq.shape[0], 2, device=positions.device, dtype=torch.float32)
+    check(lib().asb_rotary_table(ptr(table), ptr(positions), ptr(inv_freq), positions.shape[0], inv_freq.shape[0], stream()))
+    return table
+
+
 def linear_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor,
                       state_slots: torch.Tensor, req_q_start: torch.Tensor, num_requests: int, *,
                       decay: torch.Tensor | None = None, token_decay: torch.Tensor | None = None,
                       token_gain: torch.Tensor | None = None, norm_state: torch.Tensor | None = None,
                       positions: torch.Tensor | None = None, inv_freq: torch.Tensor | None = None, rotary_dim: int = 0,
                       q_scale: float = 1.0, k_scale: float = 1.0, activation: bool = False,
-                      segments: Segments | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:  # fmt: skip
+                      segments: Segments | None = None, table: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:  # fmt: skip
     """The general form of `lightning_attention`: S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = S_t^T q_t.
 
     a: `decay` float32 [H], or `token_decay` float32 [T, H]; b: `token_gain` float32 [T, H], or 1.
     `norm_state` float32 [slots, H, D]: a normaliser n_t = a_t n_(t-1) + b_t k_t is kept there too and
     n_t . q_t returned as the second result, float32 [T, H]. `positions` int32 [T] with `inv_freq`
     float32 [rotary_dim / 2]: q and k are rotated first, pairs (i, i + rotary_dim / 2) of each head's
-    first rotary_dim entries by position * inv_freq[i]. q_scale and k_scale multiply q and k after
-    that. Everything from the rotation on is float32. Returns (o float32 [T, H * V], n . q or None)."""
+    first rotary_dim entries by position * inv_freq[i] (`table`: the step's `rotary_table` of these
+    positions and frequencies, where the caller has made it already). q_scale and k_scale multiply q
+    and k after that. Everything from the rotation on is float32. Returns (o float32 [T, H * V], n . q or None)."""
     require_cuda(proj, state, state_slots, req_q_start, decay, token_decay, token_gain, norm_state, positions, inv_freq)
     if proj.dim() != 2 or not proj.is_contiguous():
         raise KernelLibraryError("linear_recurrence: proj must be a contiguous [tokens, columns] tensor")
@@ -123,11 +135,15 @@ def linear_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, st
     out = torch.empty(T, H * V, device=proj.device, dtype=torch.float32)
     nq = torch.empty(T, H, device=proj.device, dtype=torch.float32) if norm_state is not None else None
     rot = rotary_dim if positions is not None else 0
+    if rot and table is None:
+        table = rotary_table(positions[:T], inv_freq)
+    if rot and (table.dtype != torch.float32 or tuple(table.shape) != (T, rot // 2, 2) or not table.is_contiguous()):
+        raise KernelLibraryError(f"linear_recurrence: the rotation table must be contiguous float32 [{T}, {rot // 2}, 2]")
 
     def run(state_, slots_, starts_, norm_state_, count, mode):
         check(lib().asb_linear_recurrence(ptr(out), ptr(proj), proj.shape[1], q_off, k_off, v_off, ptr(state_), ptr(slots_),
                                           ptr(starts_), ptr(decay), ptr(token_decay), ptr(token_gain), ptr(norm_state_),
-                                          ptr(nq), ptr(positions), ptr(inv_freq), rot, float(q_scale), float(k_scale),
+                                          ptr(nq), ptr(table) if rot else None, rot, float(q_scale), float(k_scale),
                                           count, H, D, V, int(activation), mode, dtype_code(proj), stream()))  # fmt: skip
 
     if segments is None:

@@ -85,10 +85,16 @@ class LightningAttention(Mixer):
                                         segments=ctx.plans["lightning_segments"])  # fmt: skip
             return ops.gated_rms_norm(o, gate, self.gain, self.eps)
         rotary = self.position.fused_rotary() if self.position is not None else None
+        table = None
+        if rotary:  # the step's cosines and sines, made once for all layers that turn by these frequencies
+            key = f"rotary_table:{self.position.theta}:{rotary.rotary_dim}"
+            if key not in ctx.plans:
+                ctx.plans[key] = ops.rotary_table(ctx.positions[: proj.shape[0]], rotary.inv_freq)
+            table = ctx.plans[key]
         o, _ = ops.linear_recurrence(proj, col, col + qk, col + 2 * qk, cache.state["s"], ctx.state_slots, ctx.req_q_start,
                                      ctx.num_requests, decay=self.decay, k_scale=self.k_scale,
                                      positions=ctx.positions if rotary else None, inv_freq=rotary.inv_freq if rotary else None,
-                                     rotary_dim=rotary.rotary_dim if rotary else 0, activation=self.activation == "silu",
+                                     rotary_dim=rotary.rotary_dim if rotary else 0, table=table, activation=self.activation == "silu",
                                      segments=ctx.plans["lightning_segments"])  # fmt: skip
         return ops.head_norm_gate(o, gate, self.heads if self.head_norm == "each" else 1, gain=self.gain, eps=self.eps,
                                   gate_activation=self.gate)  # fmt: skip

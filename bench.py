@@ -722,6 +722,7 @@ def time_zogepel(widths: list[int], layers: int, steps: int, warmup: int, pk: di
         positions = i32(list(range(T)))
         segments = ops.plan_segments([T], proj.device)
         one, each = (i32([0]), i32([0, T])), (i32(list(range(B))), i32(list(range(B + 1))))
+        turns = ops.rotary_table(positions, inv_freq)  # made once per step for all layers
 
         def memory(rows, slots, starts, n, seg):
             a, b, _ = ops.capped_gates_scan(z[:rows], 0, H, H, zero, zero, 15.0, top, slots, starts, n)
@@ -730,7 +731,7 @@ def time_zogepel(widths: list[int], layers: int, steps: int, warmup: int, pk: di
 
         def retention(rows, slots, starts, n, seg):
             return ops.linear_recurrence(proj[:rows], 0, H * D, 2 * H * D, state, slots, starts, n, decay=decay, k_scale=D ** -0.5,
-                                         positions=positions, inv_freq=inv_freq, rotary_dim=D, segments=seg)  # fmt: skip
+                                         positions=positions, inv_freq=inv_freq, rotary_dim=D, table=turns[:rows], segments=seg)  # fmt: skip
 
         def lightning(rows, slots, starts, n, seg):
             return ops.lightning_attention(proj[:rows], 0, H * D, 2 * H * D, state, slots, starts, decay, n, segments=seg)

@@ -373,7 +373,13 @@ def judge(got, ref, dtype, what, lossy):
     or state is of the order of 1), and over eight positions or more, a mean error of at most 1.5
     times that of rounding alone (at least 0.02)."""
     if dtype in ("float32", torch.float32):
-        return check(got, ref, dtype, what)
+        # 5e-5 of the largest logit: where a sublayer's output is small before its norm, the norm
+        # magnifies float32 rounding too (the worst position of these models reaches 2.6e-5)
+        got = got.float().cpu()
+        assert got.shape == ref.shape and torch.isfinite(got).all(), what
+        err = float((got.double() - ref.double()).abs().max() / ref.double().abs().max())
+        assert err < 5e-5, f"{what}: relative error {err:.3g}"
+        return
     got = got.float().cpu()
     assert got.shape == ref.shape and torch.isfinite(got).all(), what
     errors = row_errors(got, ref)
