@@ -55,6 +55,7 @@ struct LightningParams {
   const float* tok_gain;    // [T, H] a weight on each token's outer product, or null: 1
   float* norm_state;        // [slots, H, D] the normaliser, or null: none is kept
   float* norm_out;          // [T, H] n_t . q_t
+  float* through;           // [R, H] with per-token decays, from-zero pass: the product of a segment's decays
   const float2* rot_table;  // [T, rot / 2] (cos, sin) of each token's angles, or null: no rotation
   int rot;
   float q_scale, k_scale;
@@ -171,22 +172,33 @@ lightning_kernel(const LightningParams p) {
     __syncthreads();
     if (keeps_norm) {
       // n_t = a_t n_(t-1) + b_t k_t and n_t . q_t, or in the carried pass the share of the n this segment started from
-      float w = weight;
-      for (int t = 0; t < nt; ++t) {
-        float part = 0.f;
-        for (int d = threadIdx.x; d < p.D; d += 32) {
-          float n = ns[d];
-          if (!p.carry) {
-            n = fmaf(decs[t], n, gains[t] * ks[t * DP + d]);
-            ns[d] = n;
+      // (a lane owns rows d = lane, lane + 32, ...: the tile's tokens are walked row by row, and the
+      // sixteen sums over the lanes are formed together afterwards, their shuffles in flight at once)
+      float part[kTokenTile];
+#pragma unroll
+      for (int t = 0; t < kTokenTile; ++t) part[t] = 0.f;
+      for (int d = threadIdx.x; d < p.D; d += 32) {
+        float n = ns[d];
+#pragma unroll
+        for (int t = 0; t < kTokenTile; ++t) {
+          if (t < nt) {
+            if (!p.carry) n = fmaf(decs[t], n, gains[t] * ks[t * DP + d]);
+            part[t] = fmaf(n, qs[t * DP + d], part[t]);
           }
-          part = fmaf(n, qs[t * DP + d], part);
         }
-        part = asb::warp_sum(part);
-        w *= decs[t];
-        if (threadIdx.x == 0) {
-          if (p.carry) p.norm_out[(size_t)(t0 + t) * p.H + h] += w * part;
-          else p.norm_out[(size_t)(t0 + t) * p.H + h] = part;
+        ns[d] = n;
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+        for (int t = 0; t < kTokenTile; ++t) part[t] += __shfl_xor_sync(0xffffffffu, part[t], off);
+      float w = weight;
+#pragma unroll
+      for (int t = 0; t < kTokenTile; ++t) {
+        w *= t < nt ? decs[t] : 1.f;
+        if (threadIdx.x == t && t < nt) {
+          if (p.carry) p.norm_out[(size_t)(t0 + t) * p.H + h] += w * part[t];
+          else p.norm_out[(size_t)(t0 + t) * p.H + h] = part[t];
         }
       }
     }
@@ -210,6 +222,8 @@ lightning_kernel(const LightningParams p) {
       }
       continue;
     }
+    if (GEN && p.through && p.zero_init && blockIdx.z == 0 && threadIdx.x == 32 % kThreads)
+      for (int t = 0; t < nt; ++t) weight *= decs[t];  // (weight is otherwise the carried pass's)
     for (int t = 0; t < nt; ++t) {
       const float vv = vs[t * CPB + cl], dec = decs[t];
       const float4* kr = reinterpret_cast<const float4*>(ks + t * DP + ds * RPT);
@@ -233,6 +247,7 @@ lightning_kernel(const LightningParams p) {
     }
   }
   if (p.carry) return;
+  if (GEN && p.through && p.zero_init && blockIdx.z == 0 && threadIdx.x == 32 % kThreads) p.through[(size_t)r * p.H + h] = weight;
   if (keeps_norm)
     for (int d = threadIdx.x; d < p.D; d += 32) np_[d] = ns[d];
 #pragma unroll
@@ -261,7 +276,7 @@ int launch(const LightningParams& p, int R, cudaStream_t stream) {
 __global__ void lightning_scan_kernel(float* __restrict__ local, float* __restrict__ state,
                                       const int* __restrict__ state_slots, const int* __restrict__ req_seg_start,
                                       const int* __restrict__ seg_bounds, const float* __restrict__ decay,
-                                      const float* __restrict__ tok_decay, int H, int DV) {
+                                      const float* __restrict__ seg_through, int H, int DV) {
   asb::pdl_wait();
   asb::pdl_launch_dependents();
   const int r = blockIdx.x, h = blockIdx.y;
@@ -281,9 +296,8 @@ __global__ void lightning_scan_kernel(float* __restrict__ local, float* __restri
         if (c >= c_end) break;
         local[((size_t)c * H + h) * DV + e] = S;
         float through;  // what is left of a state after the segment's tokens
-        if (tok_decay) {
-          through = 1.f;
-          for (int t = seg_bounds[c]; t < seg_bounds[c + 1]; ++t) through *= tok_decay[(size_t)t * H + h];
+        if (seg_through) {
+          through = seg_through[(size_t)c * H + h];
         } else {
           const float n = (float)(seg_bounds[c + 1] - seg_bounds[c]);
           through = dec == 1.f ? 1.f : expf(n * log_dec);
@@ -321,15 +335,17 @@ extern "C" int asb_rotary_table(float* table, const int* positions, const float*
 }
 
 // D * V elements per (request, head); for a normaliser, call it with its own buffers and V = 1.
+// seg_through [segments, H]: what is left of a state after each segment (the from-zero pass of
+// asb_linear_recurrence writes it when the decays are per token), or null: decay[h]^tokens.
 extern "C" int asb_recurrence_scan(float* local, float* state, const int* state_slots, const int* req_seg_start,
-                                   const int* seg_bounds, const float* decay, const float* tok_decay, int R, int H,
+                                   const int* seg_bounds, const float* decay, const float* seg_through, int R, int H,
                                    int D, int V, cudaStream_t stream) {
   if (R == 0) return 0;
-  if (!decay && !tok_decay) return asb::fail("recurrence_scan: no decay given");
+  if (!decay && !seg_through) return asb::fail("recurrence_scan: no decay given");
   const int DV = D * V;
   dim3 grid(R, H, (DV + 255) / 256 < 64 ? (DV + 255) / 256 : 64);
   asb::launch(lightning_scan_kernel, grid, 256, 0, stream, local, state, state_slots, req_seg_start, seg_bounds, decay,
-              tok_decay, H, DV);
+              seg_through, H, DV);
   return asb::check_launch("recurrence_scan");
 }
 
@@ -344,7 +360,7 @@ extern "C" int asb_lightning_scan(float* local, float* state, const int* state_s
 extern "C" int asb_linear_recurrence(float* out, const void* proj, int stride, int q_off, int k_off, int v_off,
                                      float* state, const int* state_slots, const int* req_q_start,
                                      const float* decay, const float* tok_decay, const float* tok_gain,
-                                     float* norm_state, float* norm_out, const float* rot_table,
+                                     float* norm_state, float* norm_out, float* through, const float* rot_table,
                                      int rot, float q_scale, float k_scale, int R, int H, int D, int V, int act,
                                      int mode, int dtype, cudaStream_t stream) {
   if (R == 0) return 0;
@@ -357,6 +373,7 @@ extern "C" int asb_linear_recurrence(float* out, const void* proj, int stride, i
   p.decay = decay; p.stride = stride; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off;
   p.H = H; p.D = D; p.V = V; p.act = act;
   p.tok_decay = tok_decay; p.tok_gain = tok_gain; p.norm_state = norm_state; p.norm_out = norm_out;
+  p.through = (mode == 1 && tok_decay) ? through : nullptr;
   p.rot_table = (rot_table && rot > 0) ? reinterpret_cast<const float2*>(rot_table) : nullptr; p.rot = rot;
   p.q_scale = q_scale; p.k_scale = k_scale;
   p.zero_init = mode == 1;  // mode 0: the recurrence from the slots' states; 1: from zero, per segment; 2: the carried share
@@ -387,5 +404,5 @@ extern "C" int asb_lightning_attention(float* out, const void* proj, int stride,
                                        const float* decay, int R, int H, int D, int V, int act, int mode, int dtype,
                                        cudaStream_t stream) {
   return asb_linear_recurrence(out, proj, stride, q_off, k_off, v_off, state, state_slots, req_q_start, decay, nullptr,
-                               nullptr, nullptr, nullptr, nullptr, 0, 1.f, 1.f, R, H, D, V, act, mode, dtype, stream);
+                               nullptr, nullptr, nullptr, nullptr, nullptr, 0, 1.f, 1.f, R, H, D, V, act, mode, dtype, stream);
 }

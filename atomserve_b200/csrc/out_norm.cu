@@ -154,54 +154,57 @@ __global__ void projection_norm_store_kernel(T* __restrict__ q_out, const T* __r
   }
 }
 
-// One block per request. The tokens are taken a chunk at a time through shared memory: all
-// threads turn the chunk's pre-activations into log gates, thread h < H walks the chunk in order
-// for head h (an addition and a maximum per token), all threads write the exponentials.
-constexpr int kGatePairs = 2048;  // (token, head) pairs of a chunk
-
+// One block per request, a warp per head (in turn), 32 tokens at a time: a lane turns its token's
+// pre-activations into log gates; the running maximum is a scan of the maps x -> max(x + f, i),
+// which compose as (f1, i1) then (f2, i2) = (f1 + f2, max(i1 + f2, i2)): five shuffle steps give
+// every lane the map of the group's tokens up to its own, applied to the maximum the group
+// starts from. Within a group the sums of f are grouped differently from token-by-token steps:
+// equal beyond rounding.
 __global__ void capped_gates_scan_kernel(float* __restrict__ decay, float* __restrict__ gain, float* __restrict__ top_out,
                                          const float* __restrict__ z, int z_stride, int i_off, int f_off,
                                          const float* __restrict__ i_bias, const float* __restrict__ f_bias,
                                          float* __restrict__ top_state, const int* __restrict__ state_slots,
                                          const int* __restrict__ req_q_start, int H, float cap) {
-  __shared__ float sf[kGatePairs], si[kGatePairs], st[kGatePairs];
   asb::pdl_wait();
   asb::pdl_launch_dependents();
-  const int r = blockIdx.x;
+  const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int lo = req_q_start[r], hi = req_q_start[r + 1];
   const float inv_cap = 1.f / cap;
-  const int per_chunk = kGatePairs / H;  // tokens of a chunk (H <= kGatePairs / 2)
-  float* ts = top_state + (size_t)state_slots[r] * H + threadIdx.x;
-  float top = threadIdx.x < H ? *ts : 0.f;
-  for (int c0 = lo; c0 < hi; c0 += per_chunk) {
-    const int n = min(per_chunk, hi - c0) * H;
-    for (int idx = threadIdx.x; idx < n; idx += blockDim.x) {
-      const int t = c0 + idx / H, h = idx % H;
-      const float zi = z[(size_t)t * z_stride + i_off + h] + i_bias[h];
-      const float zf = z[(size_t)t * z_stride + f_off + h] + f_bias[h];
-      const float u = cap * tanhf(zf * inv_cap);
-      si[idx] = cap * tanhf(zi * inv_cap);
-      sf[idx] = fminf(u, 0.f) - log1pf(expf(-fabsf(u)));  // log sigmoid(u)
-    }
-    __syncthreads();
-    if (threadIdx.x < H) {
-      for (int idx = threadIdx.x; idx < n; idx += H) {
-        const float carried = sf[idx] + top;
-        top = fmaxf(carried, si[idx]);
-        sf[idx] = carried;
-        st[idx] = top;
+  for (int h = warp; h < H; h += nwarps) {
+    float* ts = top_state + (size_t)state_slots[r] * H + h;
+    float top = *ts;  // the maximum before the group's first token (the same in every lane)
+    const float bi = i_bias[h], bf = f_bias[h];
+    for (int t0 = lo; t0 < hi; t0 += 32) {
+      const int t = t0 + lane;
+      const bool real = t < hi;
+      float f = 0.f, i = -INFINITY;  // the identity map for lanes past the end
+      if (real) {
+        const float u = cap * tanhf((z[(size_t)t * z_stride + f_off + h] + bf) * inv_cap);
+        f = fminf(u, 0.f) - log1pf(expf(-fabsf(u)));  // log sigmoid(u)
+        i = cap * tanhf((z[(size_t)t * z_stride + i_off + h] + bi) * inv_cap);
       }
+      float F = f, I = i;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const float pF = __shfl_up_sync(0xffffffffu, F, off), pI = __shfl_up_sync(0xffffffffu, I, off);
+        if (lane >= off) {
+          I = fmaxf(pI + F, I);
+          F = pF + F;
+        }
+      }
+      const float mine = fmaxf(top + F, I);
+      float before = __shfl_up_sync(0xffffffffu, mine, 1);
+      if (lane == 0) before = top;
+      if (real) {
+        const size_t at = (size_t)t * H + h;
+        decay[at] = expf(f + before - mine);
+        gain[at] = expf(i - mine);
+        top_out[at] = mine;
+      }
+      top = __shfl_sync(0xffffffffu, mine, 31);  // (lanes past the end carry the last real maximum)
     }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < n; idx += blockDim.x) {
-      const size_t at = (size_t)c0 * H + idx;
-      decay[at] = expf(sf[idx] - st[idx]);
-      gain[at] = expf(si[idx] - st[idx]);
-      top_out[at] = st[idx];
-    }
-    __syncthreads();
+    if (lane == 0) *ts = top;
   }
-  if (threadIdx.x < H) *ts = top;
 }
 
 template <typename T>
@@ -286,9 +289,8 @@ extern "C" int asb_capped_gates_scan(float* decay, float* gain, float* top_out, 
                                      const int* state_slots, const int* req_q_start, int R, int H, float cap,
                                      cudaStream_t stream) {
   if (R == 0) return 0;
-  if (H < 1 || H > kGatePairs / 2 || !(cap > 0.f)) return asb::fail("capped_gates_scan: %d heads, cap %f", H, cap);
-  int threads = 128;
-  while (threads < H) threads <<= 1;  // (at most 1,024)
+  if (H < 1 || !(cap > 0.f)) return asb::fail("capped_gates_scan: %d heads, cap %f", H, cap);
+  const int threads = 32 * (H < 16 ? H : 16);
   asb::launch(capped_gates_scan_kernel, R, threads, 0, stream, decay, gain, top_out, z, z_stride, i_off, f_off, i_bias,
               f_bias, top_state, state_slots, req_q_start, H, cap);
   return asb::check_launch("capped_gates_scan");

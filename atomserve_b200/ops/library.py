@@ -59,7 +59,7 @@ _SIGNATURES = {
     "asb_lightning_attention": [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "asb_lightning_scan": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "asb_recurrence_scan": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
-    "asb_linear_recurrence": [_P, _P, _I, _I, _I, _I] + [_P] * 9 + [_I, _F, _F] + [_I] * 7 + [_P],
+    "asb_linear_recurrence": [_P, _P, _I, _I, _I, _I] + [_P] * 10 + [_I, _F, _F] + [_I] * 7 + [_P],
     "asb_rotary_table": [_P, _P, _P, _I, _I, _P],
     # attention with a sink in the softmax's denominator
     "asb_paged_attention_sink": [_P] * 11 + [_I] * 10 + [_F, _I, _P],

@@ -140,10 +140,12 @@ def linear_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, st
     if rot and (table.dtype != torch.float32 or tuple(table.shape) != (T, rot // 2, 2) or not table.is_contiguous()):
         raise KernelLibraryError(f"linear_recurrence: the rotation table must be contiguous float32 [{T}, {rot // 2}, 2]")
 
+    through = None  # with per-token decays: what is left of a state after each segment
+
     def run(state_, slots_, starts_, norm_state_, count, mode):
         check(lib().asb_linear_recurrence(ptr(out), ptr(proj), proj.shape[1], q_off, k_off, v_off, ptr(state_), ptr(slots_),
                                           ptr(starts_), ptr(decay), ptr(token_decay), ptr(token_gain), ptr(norm_state_),
-                                          ptr(nq), ptr(table) if rot else None, rot, float(q_scale), float(k_scale),
+                                          ptr(nq), ptr(through), ptr(table) if rot else None, rot, float(q_scale), float(k_scale),
                                           count, H, D, V, int(activation), mode, dtype_code(proj), stream()))  # fmt: skip
 
     if segments is None:
@@ -151,10 +153,12 @@ def linear_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, st
         return out, nq
     local = torch.empty(segments.count, H, D, V, device=proj.device, dtype=torch.float32)
     local_n = torch.empty(segments.count, H, D, device=proj.device, dtype=torch.float32) if norm_state is not None else None
+    if token_decay is not None:
+        through = torch.empty(segments.count, H, device=proj.device, dtype=torch.float32)
     run(local, segments.index, segments.bounds, local_n, segments.count, 1)
     for own, kept, v in ((local, state, V), (local_n, norm_state, 1)):
         if own is not None:
             check(lib().asb_recurrence_scan(ptr(own), ptr(kept), ptr(state_slots), ptr(segments.req_start), ptr(segments.bounds),
-                                            ptr(decay), ptr(token_decay), num_requests, H, D, v, stream()))  # fmt: skip
+                                            ptr(decay), ptr(through), num_requests, H, D, v, stream()))  # fmt: skip
     run(local, segments.index, segments.bounds, local_n, segments.count, 2)
     return out, nq
