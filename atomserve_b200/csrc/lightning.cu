@@ -177,6 +177,7 @@ lightning_kernel(const LightningParams p) {
       float part[kTokenTile];
 #pragma unroll
       for (int t = 0; t < kTokenTile; ++t) part[t] = 0.f;
+      const float n_so_far = (p.carry && (int)threadIdx.x < nt) ? p.norm_out[(size_t)(t0 + threadIdx.x) * p.H + h] : 0.f;
       for (int d = threadIdx.x; d < p.D; d += 32) {
         float n = ns[d];
 #pragma unroll
@@ -197,14 +198,20 @@ lightning_kernel(const LightningParams p) {
       for (int t = 0; t < kTokenTile; ++t) {
         w *= t < nt ? decs[t] : 1.f;
         if (threadIdx.x == t && t < nt) {
-          if (p.carry) p.norm_out[(size_t)(t0 + t) * p.H + h] += w * part[t];
-          else p.norm_out[(size_t)(t0 + t) * p.H + h] = part[t];
+          p.norm_out[(size_t)(t0 + t) * p.H + h] = p.carry ? fmaf(w, part[t], n_so_far) : part[t];
         }
       }
     }
     if (p.carry) {
       // o_t += decay^(t - first + 1) * S_first^T q_t: what the tokens before this segment contribute
-      for (int t = 0; t < nt; ++t) {
+      // (the tile's outputs so far are fetched together first, so that no token waits for its own)
+      float so_far[kTokenTile];
+#pragma unroll
+      for (int t = 0; t < kTokenTile; ++t)
+        so_far[t] = (ds == 0 && live && t < nt) ? p.out[(size_t)(t0 + t) * p.H * p.V + h * p.V + col] : 0.f;
+#pragma unroll
+      for (int t = 0; t < kTokenTile; ++t) {
+        if (t >= nt) break;
         const float4* qr = reinterpret_cast<const float4*>(qs + t * DP + ds * RPT);
         float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -218,7 +225,7 @@ lightning_kernel(const LightningParams p) {
         float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
         for (int off = 1; off < DS; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
         weight *= decs[t];
-        if (ds == 0 && live) p.out[(size_t)(t0 + t) * p.H * p.V + h * p.V + col] += weight * o;
+        if (ds == 0 && live) p.out[(size_t)(t0 + t) * p.H * p.V + h * p.V + col] = fmaf(weight, o, so_far[t]);
       }
       continue;
     }

@@ -344,7 +344,7 @@ def test_sink_attention_part_alone(dtype):
 
 # ---- whole models through the step function ---------------------------------------------------
 
-LENGTHS = {"a": [5, 49, 130, 1, 64], "b": [33, 2, 97, 40], "c": [300, 9, 70]}
+LENGTHS = {"a": [5, 49, 130, 1, 64], "b": [33, 2, 97, 40], "c": [300, 9, 70], "d": [20, 3, 70], "e": [45, 2, 90]}
 
 
 def oracle(cfg, w, prompt):
@@ -453,7 +453,8 @@ def test_mixed_requests_reusing_pages_and_slots(models, name, dtype):
             judge(logits[row : row + n], refs3[e["id"]][e["at"] : e["at"] + n], dtype, f"{name} request {e['id']} at {e['at']}",
                   tols3[e["id"]][e["at"] : e["at"] + n])
             row += n
-    assert sum(len(p) for p in ps3) > rp.cache.num_blocks * bs, "the pool was large enough to never reuse a page"
+    if rp.cache.groups:  # (a model of matrix memories alone keeps no pages, only slots)
+        assert sum(len(p) for p in ps3) > rp.cache.num_blocks * bs, "the pool was large enough to never reuse a page"
     assert len(ps3) > 4
 
 

@@ -60,4 +60,21 @@ ZOGEPEL_C = dict(
 )  # fmt: skip
 BLOCK_SIZE_C = 16
 
-ZOGEPEL = {"a": (ZOGEPEL_A, BLOCK_SIZE_A), "b": (ZOGEPEL_B, BLOCK_SIZE_B), "c": (ZOGEPEL_C, BLOCK_SIZE_C)}
+# matrix memories only (no layer keeps pages), a width that is no multiple of 8, one head, a tiny token input
+ZOGEPEL_D = dict(
+    architecture="Zogepel", vocab=130, width=100, residual_mult=0.9, norm=dict(eps=1e-5), embedding=dict(scale=3.0),
+    token_side=dict(dim=5),
+    layers=[_mlstm(1, 40, 56, 9.0, 60), _mlstm(3, 12, 20, 5.0, None)],
+)  # fmt: skip
+BLOCK_SIZE_D = 16
+
+# attention beside retention only, a window of one token in one layer
+ZOGEPEL_E = dict(
+    architecture="Zogepel", vocab=140, width=48, residual_mult=0.8, norm=dict(eps=1e-5), embedding=dict(scale=2.0),
+    layers=[_parallel(_left(2, 2, 8, 1, 0.9), _right(2, 4, 4, [0.9, 0.5], 30.0, 2), 56),
+            _parallel(_left(4, 2, 12, 37, 0.5), _right(1, 20, 36, [0.98], 300.0, 20), None)],
+)  # fmt: skip
+BLOCK_SIZE_E = 8
+
+ZOGEPEL = {"a": (ZOGEPEL_A, BLOCK_SIZE_A), "b": (ZOGEPEL_B, BLOCK_SIZE_B), "c": (ZOGEPEL_C, BLOCK_SIZE_C),
+           "d": (ZOGEPEL_D, BLOCK_SIZE_D), "e": (ZOGEPEL_E, BLOCK_SIZE_E)}
