@@ -25,6 +25,7 @@
 //   asb_gated_token_slice    act(z) * table[token, offset : offset + dim]: the gate of a per-layer
 //                            token input.
 #include "common.cuh"
+#include "gemm_partials.cuh"
 
 namespace {
 
@@ -82,6 +83,61 @@ __global__ void residual_out_norm_kernel(float* __restrict__ out32, T* __restric
     if (out32) out32[dst + i] = v;
     if (out_c) out_c[dst + i] = asb::from_float<T>(v);
   }
+}
+
+// asb_residual_out_norm with y given as the partial sums that the tensor-core GEMM left in its
+// workspace (few tokens): a thread adds up the slots of 8 columns itself, in the reduction's order,
+// so the GEMM's reduction kernel and a round trip of y through memory fall away.
+__global__ void partial_residual_out_norm_kernel(float* __restrict__ out32, __nv_bfloat16* __restrict__ out_c,
+                                                 const asb::PartialSums ps, const float* __restrict__ x,
+                                                 const float* __restrict__ gain, const float* __restrict__ scale,
+                                                 int width, float mult, float eps, int centred) {
+  __shared__ float scratch[32];
+  const int t = blockIdx.x, i = threadIdx.x * 8;
+  const bool active = i < width;
+  const int slots = active ? asb::partial_slots(ps, i / asb::kPartialRows) : 0;
+  asb::pdl_wait();
+  asb::pdl_launch_dependents();
+  float y[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) y[k] = 0.f;
+  if (active) asb::partial_sum<8>(ps, t, i, slots, y);
+  const float inv_w = 1.f / (float)width;
+  float mean = 0.f;
+  if (centred) {
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s += y[k];
+    mean = asb::block_sum(s, scratch) * inv_w;
+  }
+  float ss = 0.f;
+  if (active) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float d = y[k] - mean;
+      ss = fmaf(d, d, ss);
+    }
+  }
+  const float inv = 1.f / sqrtf(asb::block_sum(ss, scratch) * inv_w + eps);
+  if (!active) return;
+  const float4 g0 = *reinterpret_cast<const float4*>(gain + i), g1 = *reinterpret_cast<const float4*>(gain + i + 4);
+  const float4 x0 = *reinterpret_cast<const float4*>(x + (size_t)t * width + i);
+  const float4 x1 = *reinterpret_cast<const float4*>(x + (size_t)t * width + i + 4);
+  const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+  const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+  float v[8];
+  uint4 packed;
+  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&packed);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    float n = (y[k] - mean) * inv * g[k];
+    if (scale) n *= scale[i + k];
+    v[k] = fmaf(mult, n, xs[k]);
+    o[k] = __float2bfloat16_rn(v[k]);
+  }
+  *reinterpret_cast<float4*>(out32 + (size_t)t * width + i) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(out32 + (size_t)t * width + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  *reinterpret_cast<uint4*>(out_c + (size_t)t * width + i) = packed;
 }
 
 // One block per token, a warp per head (in turn). TO: the type of o.
@@ -248,6 +304,27 @@ extern "C" int asb_residual_out_norm(float* out32, void* out_c, const float* x, 
                 width, mult, eps, centred);
   });
   return asb::check_launch("residual_out_norm");
+}
+
+// out32 (float32) and out_c (bfloat16) = x + mult * N(y) * gain * scale, y being the partial sums of
+// asb_gemm_tcgen05 mode 3 on [tokens, K] x [width, K]. Widths that are a multiple of 8 up to 8192,
+// pointers 16-byte aligned. scale may be null.
+extern "C" int asb_partial_residual_out_norm(float* out32, void* out_c, const float* ws, int max_slots, int bn,
+                                             int kb_per_tile, int num_tiles, int blocks, const float* x,
+                                             const float* gain, const float* scale, int tokens, int width, float mult,
+                                             float eps, int centred, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (width % 8 || width / 8 > 1024) return asb::fail("partial_residual_out_norm: width %d must be a multiple of 8 up to 8192", width);
+  if (tokens > bn || num_tiles * asb::kPartialRows < width)
+    return asb::fail("partial_residual_out_norm: %d tokens x %d columns do not fit the partial sums (%d x %d)", tokens, width, bn,
+                     num_tiles * asb::kPartialRows);
+  if (((uintptr_t)out32 | (uintptr_t)out_c | (uintptr_t)x | (uintptr_t)gain | (uintptr_t)ws) & 15)
+    return asb::fail("partial_residual_out_norm: pointers must be 16-byte aligned");
+  const asb::PartialSums ps = {ws, max_slots, bn, kb_per_tile, num_tiles, blocks};
+  const int threads = ((width / 8) + 31) / 32 * 32;
+  asb::launch(partial_residual_out_norm_kernel, tokens, threads, 0, stream, out32, (__nv_bfloat16*)out_c, ps, x, gain, scale,
+              width, mult, eps, centred);
+  return asb::check_launch("partial_residual_out_norm");
 }
 
 // o: [n, heads * width], float32 (o_dtype 0) or the compute dtype (1: as `dtype`). gate: rows of

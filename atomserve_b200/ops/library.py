@@ -67,6 +67,7 @@ _SIGNATURES = {
     "asb_prefill_attention_tcgen05_sink": [_P] * 8 + [_I] * 9 + [_F, _P, _P],
     # blocks with the norm on the sublayer's output, and their mixers
     "asb_residual_out_norm": [_P] * 10 + [_I, _I, _F, _F, _I, _I, _P],
+    "asb_partial_residual_out_norm": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _F, _F, _I, _P],
     "asb_head_norm_gate": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _I, _P],
     "asb_projection_norm_store": [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "asb_capped_gates_scan": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _F, _P],

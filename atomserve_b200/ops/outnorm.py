@@ -6,6 +6,7 @@ from __future__ import annotations
 import torch
 
 from atomserve_b200.ops.library import KernelLibraryError, check, dtype_code, lib, ptr, require_cuda, stream
+from atomserve_b200.ops.linear import PartialSums
 
 
 def _f32_rows(x: torch.Tensor | None, name: str, shape: tuple | None = None) -> None:
@@ -15,15 +16,28 @@ def _f32_rows(x: torch.Tensor | None, name: str, shape: tuple | None = None) -> 
         raise KernelLibraryError(f"{name} must be contiguous float32{'' if shape is None else ' ' + str(list(shape))}, got {x.dtype} {tuple(x.shape)}")
 
 
-def residual_out_norm(x: torch.Tensor | None, y: torch.Tensor, gain: torch.Tensor, eps: float, dtype: torch.dtype, *,
+def residual_out_norm(x: torch.Tensor | None, y: torch.Tensor | PartialSums, gain: torch.Tensor, eps: float, dtype: torch.dtype, *,
                       mult: float = 1.0, scale: torch.Tensor | None = None, centred: bool = True,
                       halves: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
                       rows: torch.Tensor | None = None, want_stream: bool = True) -> tuple[torch.Tensor | None, torch.Tensor]:  # fmt: skip
     """out = x + mult * N(y) * gain * scale, with N the centred norm (y - mean) / sqrt(var + eps) or,
     `centred=False`, y / sqrt(mean(y^2) + eps). x (float32 [N, width]) absent: the norm alone.
     `halves=(b, gain_a, gain_b)`: y stands for (R(y) gain_a + R(b) gain_b) / 2, R the unit-RMS norm.
-    `rows` (int32) picks source rows. Returns (out as float32 or None, out in `dtype`); with dtype
-    float32 both are one tensor."""
+    `rows` (int32) picks source rows. y may also be the partial sums of a product
+    (`linear_for_stream`), which the kernel then adds up itself. Returns (out as float32 or None, out
+    in `dtype`); with dtype float32 both are one tensor."""
+    if isinstance(y, PartialSums):
+        require_cuda(x, gain, scale)
+        _f32_rows(x, "x", (y.tokens, y.columns))
+        _f32_rows(gain, "gain", (y.columns,))
+        _f32_rows(scale, "scale", (y.columns,))
+        if x is None or rows is not None or halves is not None or dtype != torch.bfloat16:
+            raise KernelLibraryError("partial sums are normed and added to all rows of a stream of their shape, for bfloat16 products")
+        out32 = torch.empty_like(x)
+        out_c = torch.empty_like(x, dtype=dtype)
+        check(lib().asb_partial_residual_out_norm(ptr(out32), ptr(out_c), ptr(y.workspace), *y.layout(), ptr(x), ptr(gain),
+                                                  ptr(scale), x.shape[0], x.shape[1], float(mult), float(eps), int(centred), stream()))  # fmt: skip
+        return out32, out_c
     b, gain_a, gain_b = halves if halves is not None else (None, None, None)
     require_cuda(x, y, gain, scale, rows, b, gain_a, gain_b)
     if y.dim() != 2:

@@ -93,9 +93,14 @@ class OutputNormBlock(PostNormBlock):
             y, rest = halves(h, ctx, cache, write_cache)
             x, h = self.mixer_norm.add_forward(x, y, rest)
         else:
-            x, h = self.mixer_norm.add_forward(x, self.mixer.forward(h, None, ctx, cache, write_cache))
+            # a sublayer that offers `forward_for_stream` may hand its last product over as the GEMM's
+            # partial sums, which the norm's kernel then adds up itself (nothing runs in between)
+            mix = getattr(self.mixer, "forward_for_stream", None)
+            y = mix(h, ctx, cache, write_cache) if mix is not None else self.mixer.forward(h, None, ctx, cache, write_cache)
+            x, h = self.mixer_norm.add_forward(x, y)
         if self.has_feed_forward:
-            x, h = self.feed_forward_norm.add_forward(x, self.feed_forward.forward(h, None, ctx))
+            ff = getattr(self.feed_forward, "forward_for_stream", None)
+            x, h = self.feed_forward_norm.add_forward(x, ff(h, ctx) if ff is not None else self.feed_forward.forward(h, None, ctx))
         if self.token_input is not None:
             x, h = self.token_input.forward(x, h, ctx)
         return x, h

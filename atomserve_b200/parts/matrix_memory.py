@@ -77,5 +77,10 @@ class MatrixMemory(Mixer):
         # without a residual (a block that sums in float32 itself) the product stays float32
         return ops.linear(self.mixed(h, ctx, cache), self.o_proj, residual, out_dtype=torch.float32 if residual is None else None)
 
+    def forward_for_stream(self, h: torch.Tensor, ctx: StepContext, cache: CacheView | None, write_cache: bool = True):
+        """mix(h) for a block that norms it and adds it to a float32 stream at once: float32, or the
+        output projection's partial sums for that norm to add up (`ops.linear_for_stream`)."""
+        return ops.linear_for_stream(self.mixed(h, ctx, cache), self.o_proj)
+
 
 register_part("mixer", "matrix_memory", MatrixMemory)

@@ -46,7 +46,7 @@ class GatedTokenSlice(TokenInput):
     def forward(self, x: torch.Tensor, h: torch.Tensor, ctx: StepContext) -> tuple[torch.Tensor, torch.Tensor]:
         z = ops.linear(h, self.gate, out_dtype=torch.float32)
         gated = ops.gated_token_slice(z, self.table, ctx.token_ids, self.offset)
-        y = ops.linear(gated, self.proj, out_dtype=torch.float32)
+        y = ops.linear_for_stream(gated, self.proj)  # float32, or partial sums for the norm to add up
         return ops.residual_out_norm(x, y, self.gain, self.eps, self.dtype, mult=self.mult, centred=False)
 
 

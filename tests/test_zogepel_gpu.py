@@ -63,6 +63,32 @@ def test_norm_on_the_sublayers_output(dtype, d):
     check(last, plain.layer_norm(y.double(), gain.double(), EPS).float()[[7, 0, 3]], dtype, "the norm alone on chosen rows", 0.01)
 
 
+def test_output_norm_reading_a_products_partial_sums():
+    """With few tokens the last product of a sublayer stays as the GEMM's partial sums and the
+    norm's kernel adds them up: the finished product followed by the norm, up to the order in
+    which a row's sums are formed (a few float32 ulps; the bfloat16 copy within one of its own)."""
+    from atomserve_b200 import ops
+    from atomserve_b200.ops.linear import PartialSums
+
+    g = torch.Generator().manual_seed(4)
+    met = 0
+    for T, d, K in ((1, 256, 512), (5, 320, 1024), (8, 2048, 2048), (33, 256, 384)):
+        inner = (torch.randn(T, K, generator=g)).bfloat16().cuda()
+        w = (torch.randn(d, K, generator=g) * K**-0.5).bfloat16().cuda()
+        x = torch.randn(T, d, generator=g).cuda()
+        gain, scale = ((1 + 0.1 * torch.randn(d, generator=g)).cuda() for _ in range(2))
+        for centred, sc in ((True, scale), (False, None)):
+            whole = ops.residual_out_norm(x, ops.linear(inner, w, out_dtype=torch.float32), gain, EPS, torch.bfloat16, mult=0.7,
+                                          scale=sc, centred=centred)  # fmt: skip
+            y = ops.linear_for_stream(inner, w)
+            met += isinstance(y, PartialSums)
+            fused = ops.residual_out_norm(x, y, gain, EPS, torch.bfloat16, mult=0.7, scale=sc, centred=centred)
+            what = f"{T} tokens, width {d}, K {K}, centred {centred}"
+            assert float((whole[0] - fused[0]).abs().max() / whole[0].abs().max()) < 2e-6, what
+            assert bool(((whole[1].float() - fused[1].float()).abs() <= 2.0**-7 * whole[1].float().abs() + 1e-30).all()), what
+    assert met, "no shape ran with partial sums"
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("d,dim,layers,layer", [(96, 12, 4, 2), (256, 16, 3, 0), (64, 1, 2, 1)])
 def test_token_input_alone(dtype, d, dim, layers, layer):
@@ -252,11 +278,14 @@ def attend(q_parts, pages, requests, lens, starts, window, scale, sink):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,KV,hd,bs,window", [(6, 2, 24, 16, 20), (4, 4, 96, 8, 7), (8, 2, 64, 16, 100), (4, 1, 128, 16, 33), (3, 3, 40, 4, 600)])
+@pytest.mark.parametrize("H,KV,hd,bs,window", [(6, 2, 24, 16, 20), (4, 4, 96, 8, 7), (8, 2, 64, 16, 100), (4, 1, 128, 16, 33), (3, 3, 40, 4, 600),
+                                               (8, 2, 128, 16, 600), (4, 2, 64, 16, 650), (32, 1, 64, 16, 300)])
 def test_attention_with_a_sink(dtype, H, KV, hd, bs, window):
     """Random queries and keys with sinks from far below to far above the scores: a whole prompt,
     its last tokens alone (decoding), and two requests in one step, against the plain softmax with
-    the sink in its denominator. Long enough for several key partitions."""
+    the sink in its denominator. Long enough for several key partitions, in the general kernel and
+    (bfloat16, heads of 64 and 128) in the tensor-core kernels, also with more query heads a kv head
+    than a tile of those has rows."""
     g = torch.Generator().manual_seed(H + hd)
     T, scale = 700, 2.0 * hd**-0.5
     sink = torch.linspace(-6, 6, H)
@@ -277,7 +306,7 @@ def test_attention_with_a_sink(dtype, H, KV, hd, bs, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("window,bs,hd", [(96, 16, 32), (7, 8, 32), (33, 16, 128), (16, 16, 64), (100, 16, 128)])
+@pytest.mark.parametrize("window,bs,hd", [(96, 16, 32), (7, 8, 32), (33, 16, 128), (16, 16, 64), (100, 16, 128), (250, 16, 128), (290, 16, 64)])
 def test_one_key_stands_out_at_the_windows_edges_and_the_sink_counts_once(dtype, window, bs, hd):
     """All keys are zero but one whose score is large; its value is e_1. For a query at position p
     the key at p - window + 1 is the last one seen and the key at p - window the first one not
