@@ -56,7 +56,7 @@ constexpr int BM = 128;   // P rows per tile = TMEM lanes
 constexpr int BK = 64;    // K elements per stage: 128 bytes, one swizzle atom
 constexpr int UMMA_K = 16;
 
-enum Epilogue : int { kStoreBf16 = 0, kStoreBf16Residual = 1, kStoreF32 = 2, kStoreSwiGLU = 4, kPartialsOnly = 8 };
+enum Epilogue : int { kStoreBf16 = 0, kStoreBf16Residual = 1, kStoreF32 = 2, kStoreSwiGLU = 4, kPartialsOnly = 8, kStoreBf16Relu2 = 16 };
 
 struct GemmParams {
   void* out;             // bf16 or f32 [M, N]
@@ -166,6 +166,7 @@ struct Config {
 
 // SwiGLU on a (gate, up) pair of float32 sums (atomserve/kernels.py:437-449).
 __device__ __forceinline__ float swiglu(float gate, float up) { return gate / (1.f + __expf(-gate)) * up; }
+__device__ __forceinline__ float relu2(float v) { v = fmaxf(v, 0.f); return v * v; }  // kStoreBf16Relu2: max(v, 0)^2 on the float32 sums
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -402,6 +403,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 ((float*)p.out)[at] = v;
               } else {
                 if (p.epilogue == kStoreBf16Residual) v += __bfloat162float(((const __nv_bfloat16*)p.residual)[at]);
+                else if (p.epilogue == kStoreBf16Relu2) v = relu2(v);
                 ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(v);
               }
             }
@@ -437,6 +439,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
               for (int j = 0; j < kChunk; j += 2) {
                 float a = __uint_as_float(raw[j]), b = __uint_as_float(raw[j + 1]);
                 if (res) { a += __bfloat162float(rb[j]); b += __bfloat162float(rb[j + 1]); }
+                if (p.epilogue == kStoreBf16Relu2) { a = relu2(a); b = relu2(b); }
                 ob[j >> 1] = __floats2bfloat162_rn(a, b);
               }
 #pragma unroll
@@ -447,6 +450,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 if (j < valid) {
                   float v = __uint_as_float(raw[j]);
                   if (res) v += __bfloat162float(res[j]);
+                  if (p.epilogue == kStoreBf16Relu2) v = relu2(v);
                   o[j] = __float2bfloat16_rn(v);
                 }
             }
@@ -532,6 +536,7 @@ __global__ void segment_reduce_kernel(const GemmParams p, int parts) {
       ((float*)p.out)[at] = o;
     } else {
       if (p.epilogue == kStoreBf16Residual) o += __bfloat162float(((const __nv_bfloat16*)p.residual)[at]);
+      else if (p.epilogue == kStoreBf16Relu2) o = relu2(o);
       ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(o);
     }
   }
@@ -777,7 +782,8 @@ extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const v
                                 int N, int K, int mode, float* workspace, int* status,
                                 cudaStream_t stream) {
   const int out_f32 = mode == 1;
-  if (mode < 0 || mode > 3) return asb::fail("gemm_tcgen05: unknown mode %d", mode);
+  if (mode < 0 || mode > 4) return asb::fail("gemm_tcgen05: unknown mode %d", mode);
+  if (mode == 4 && residual) return asb::fail("gemm_tcgen05: the squared-ReLU form takes no residual");
   if (mode == 3 && residual) return asb::fail("gemm_tcgen05: the partial-sum form takes no residual");
   if (mode == 2 && (residual || N % 2)) return asb::fail("gemm_tcgen05: the SwiGLU form takes no residual and an even N");
   if (M == 0 || N == 0) return 0;
@@ -801,7 +807,7 @@ extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const v
   p.ldo = N;
   p.p_rows = pl.swap ? N : M;
   p.q_rows = pl.swap ? M : N;
-  p.epilogue = mode == 3 ? kPartialsOnly : mode == 2 ? kStoreSwiGLU : (out_f32 ? kStoreF32 : (residual ? kStoreBf16Residual : kStoreBf16));
+  p.epilogue = mode == 4 ? kStoreBf16Relu2 : mode == 3 ? kPartialsOnly : mode == 2 ? kStoreSwiGLU : (out_f32 ? kStoreF32 : (residual ? kStoreBf16Residual : kStoreBf16));
   p.tiles_p = pl.tiles_p;
   p.num_tiles = pl.tiles_p * pl.tiles_q;
   p.kb_per_tile = pl.kb_per_tile;

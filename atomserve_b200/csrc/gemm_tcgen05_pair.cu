@@ -35,7 +35,7 @@ constexpr int UMMA_K = 16;
 constexpr int kMaxLoaders = 4;   // threads that request operands, a warp each: warps 0, 6, 7, 8
 constexpr int kThreads = 192 + 32 * (kMaxLoaders - 1);
 
-enum Epilogue : int { kStoreBf16 = 0, kStoreBf16Residual = 1, kStoreF32 = 2, kStoreSwiGLU = 4 };
+enum Epilogue : int { kStoreBf16 = 0, kStoreBf16Residual = 1, kStoreF32 = 2, kStoreSwiGLU = 4, kStoreBf16Relu2 = 16 };
 
 struct PairParams {
   void* out;             // bf16 [M, N], f32 [M, N], or bf16 [M, N / 2] (SwiGLU)
@@ -78,6 +78,7 @@ struct PairConfig {
 };
 
 __device__ __forceinline__ float swiglu(float gate, float up) { return gate / (1.f + __expf(-gate)) * up; }
+__device__ __forceinline__ float relu2(float v) { v = fmaxf(v, 0.f); return v * v; }  // kStoreBf16Relu2
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -366,6 +367,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
           for (int j = 0; j < 32; j += 2) {
             float a = __uint_as_float(raw[j]), b = __uint_as_float(raw[j + 1]);
             if (res) { a += __bfloat162float(rb[j]); b += __bfloat162float(rb[j + 1]); }
+            if (p.epilogue == kStoreBf16Relu2) { a = relu2(a); b = relu2(b); }
             ob[j >> 1] = __floats2bfloat162_rn(a, b);
           }
 #pragma unroll
@@ -376,6 +378,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             if (j < valid) {
               float v = __uint_as_float(raw[j]);
               if (res) v += __bfloat162float(res[j]);
+              if (p.epilogue == kStoreBf16Relu2) v = relu2(v);
               o[j] = __float2bfloat16_rn(v);
             }
         }
@@ -436,6 +439,7 @@ __global__ void tail_reduce_kernel(const PairParams p) {
       ((float*)p.out)[at + k] = o;
     } else {
       if (p.epilogue == kStoreBf16Residual) o += __bfloat162float(((const __nv_bfloat16*)p.residual)[at + k]);
+      else if (p.epilogue == kStoreBf16Relu2) o = relu2(o);
       ((__nv_bfloat16*)p.out)[at + k] = __float2bfloat16_rn(o);
     }
   }
@@ -529,7 +533,8 @@ extern "C" long long asb_gemm_tcgen05_pair_cut(int M, int N, int K, int bn, int*
 // workspace: float32, asb_gemm_tcgen05_pair_cut(M, N, K, bn) elements (null if that is 0).
 extern "C" int asb_gemm_tcgen05_pair(void* out, const void* x, const void* w, const void* residual, int M, int N,
                                      int K, int mode, int bn, float* workspace, int* status, cudaStream_t stream) {
-  if (mode < 0 || mode > 2) return asb::fail("gemm_tcgen05_pair: unknown mode %d", mode);
+  if (mode < 0 || mode == 3 || mode > 4) return asb::fail("gemm_tcgen05_pair: unknown mode %d", mode);
+  if (mode == 4 && residual) return asb::fail("gemm_tcgen05_pair: the squared-ReLU form takes no residual");
   if (mode == 2 && (residual || N % 2)) return asb::fail("gemm_tcgen05_pair: the SwiGLU form takes no residual and an even N");
   if (mode == 1 && residual) return asb::fail("gemm_tcgen05_pair: the float32 result form takes no residual");
   if (M == 0 || N == 0) return 0;
@@ -545,7 +550,7 @@ extern "C" int asb_gemm_tcgen05_pair(void* out, const void* x, const void* w, co
   p.M = M;
   p.N = N;
   p.ldo = N;
-  p.epilogue = mode == 2 ? kStoreSwiGLU : (mode == 1 ? kStoreF32 : (residual ? kStoreBf16Residual : kStoreBf16));
+  p.epilogue = mode == 4 ? kStoreBf16Relu2 : mode == 2 ? kStoreSwiGLU : (mode == 1 ? kStoreF32 : (residual ? kStoreBf16Residual : kStoreBf16));
   p.bn = bn;
   p.tiles_m = (M + 255) / 256;
   p.num_tiles = p.tiles_m * ((N + bn - 1) / bn);

@@ -78,9 +78,10 @@ _WORKSPACE_FLOATS: dict[tuple[int, int, int], int] = {}
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None, out_dtype: torch.dtype,
-                 swiglu: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:  # fmt: skip
+                 swiglu: bool = False, out: torch.Tensor | None = None, relu2: bool = False) -> torch.Tensor:  # fmt: skip
     """bfloat16 x [M, K] . w [N, K]^T on tcgen05 tensor cores (TMA operands, TMEM accumulator).
-    swiglu: the rows of w alternate gate and up; returns silu(gate) * up, [M, N / 2]."""
+    swiglu: the rows of w alternate gate and up; returns silu(gate) * up, [M, N / 2].
+    relu2: max(., 0)^2 of the float32 sums before the one rounding to bfloat16."""
     M, K = x.shape
     N = w.shape[0]
     if out is None:
@@ -91,7 +92,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None
         query.restype = ctypes.c_longlong
         need = _WORKSPACE_FLOATS[(M, N, K)] = query(M, N, K, None)
     workspace = gemm_workspace(x.device, need) if need else None
-    check(lib().asb_gemm_tcgen05(ptr(out), ptr(x), ptr(w), ptr(residual), M, N, K, 2 if swiglu else int(out_dtype == torch.float32),
+    check(lib().asb_gemm_tcgen05(ptr(out), ptr(x), ptr(w), ptr(residual), M, N, K, 4 if relu2 else 2 if swiglu else int(out_dtype == torch.float32),
                                  ptr(workspace), ptr(gemm_status(x.device)), stream()))  # fmt: skip
     return out
 
@@ -201,6 +202,20 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
     if x.dtype != torch.bfloat16 or not swiglu_fusable(w_interleaved) or not x.is_contiguous() or x.data_ptr() % 16:
         raise KernelLibraryError("linear_swiglu takes contiguous bfloat16 operands with K a multiple of 8")
     return gemm_tcgen05(x, w_interleaved, None, torch.bfloat16, swiglu=True)
+
+
+def linear_relu2(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor | None:
+    """max(x . w^T, 0)^2 in one kernel: the squared ReLU applied to the float32 sums in the
+    tensor-core GEMM's epilogue, before the one rounding to bfloat16 (the unfused path rounds the
+    product first). None where the product does not run on that kernel (float32, another backend,
+    shapes it refuses): the caller then multiplies and activates in turn."""
+    if BACKEND != "tcgen05" or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not x.is_cuda:
+        return None
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1] or not x.is_contiguous() or not w.is_contiguous():
+        return None
+    if not tcgen05_supported(x, w):
+        return None
+    return gemm_tcgen05(x, w, None, torch.bfloat16, relu2=True)
 
 
 def linear(

@@ -38,15 +38,23 @@ class GeluMLP(FeedForward):
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         self.up, self.down = tensors[self.prefix + "up"], tensors[self.prefix + "down"]
 
+    def inner(self, h: torch.Tensor) -> torch.Tensor:
+        """act(up h): the squared ReLU inside the product's epilogue where the tensor-core GEMM runs it."""
+        if self.activation == "relu2":
+            fused = ops.linear_relu2(h, self.up)
+            if fused is not None:
+                return fused
+        return ops.activation(ops.linear(h, self.up), self.activation)
+
     def forward(self, h: torch.Tensor, residual: torch.Tensor | None, ctx: StepContext) -> torch.Tensor:
-        inner = ops.activation(ops.linear(h, self.up), self.activation)
+        inner = self.inner(h)
         # without a residual (a block that sums in float32 itself) the product stays float32
         return ops.linear(inner, self.down, residual, out_dtype=torch.float32 if residual is None else None)
 
     def forward_for_stream(self, h: torch.Tensor, ctx: StepContext):
         """ff(h) for a block that adds it to a float32 stream and norms the sum at once: float32, or
         the down projection's partial sums for that norm to add up (`ops.linear_for_stream`)."""
-        return ops.linear_for_stream(ops.activation(ops.linear(h, self.up), self.activation), self.down)
+        return ops.linear_for_stream(self.inner(h), self.down)
 
 
 class RoutedExperts(FeedForward):

@@ -63,6 +63,33 @@ def test_norm_on_the_sublayers_output(dtype, d):
     check(last, plain.layer_norm(y.double(), gain.double(), EPS).float()[[7, 0, 3]], dtype, "the norm alone on chosen rows", 0.01)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 384, 320), (8, 8192, 2048), (33, 100, 64), (200, 1024, 512), (600, 768, 256), (2048, 4096, 1024), (1024, 5000, 2048)])
+def test_squared_relu_in_the_products_epilogue(M, N, K):
+    """max(x W^T, 0)^2 from the tensor-core GEMMs' epilogues (few tokens with K cut and a reduction
+    kernel, single SMs, pairs of SMs, a last round cut along K) against float64, rounded once."""
+    from atomserve_b200 import ops
+
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * K**-0.5).bfloat16()
+    got = ops.linear_relu2(x.cuda(), w.cuda())
+    assert got is not None and got.dtype == torch.bfloat16
+    ref = torch.relu(x.double() @ w.double().T) ** 2
+    err = (got.double().cpu() - ref).abs()
+    assert bool((err <= 2.0**-8 * ref.abs() + 1e-4).all()), float((err / (ref.abs() + 1e-3)).max())
+    part = build_relu2_mlp(K, N, x, w)
+    assert torch.equal(part, got.cpu())
+
+
+def build_relu2_mlp(K, N, x, w):
+    """The feed-forward part's inner activation: the fused product."""
+    from atomserve_b200.parts import PartSpec, build_part
+
+    part = build_part("feed_forward", PartSpec("activation_mlp", dict(intermediate_size=N, activation="relu2"), "f."), K)
+    part.load({"f.up": w.cuda(), "f.down": torch.zeros(K, N, dtype=torch.bfloat16, device="cuda")})
+    return part.inner(x.cuda()).cpu()
+
+
 def test_output_norm_reading_a_products_partial_sums():
     """With few tokens the last product of a sublayer stays as the GEMM's partial sums and the
     norm's kernel adds them up: the finished product followed by the norm, up to the order in
