@@ -690,7 +690,7 @@ def zogepel_shape(width: int, layers: int) -> dict:
                          rot=dict(base=10000.0, dims=64))
             mixer = dict(type="parallel", mixer=dict(left=left, right=right))
         out.append(dict(mixer, mlp=dict(kind="dense", ff=4 * width)))
-    return dict(architecture="Zogepel", vocab=32000, width=width, layers=out, norm=dict(eps=1e-6), residual_mult=0.7,
+    return dict(architecture="Zogepel", vocab=32000, width=width, layers=out, norm=dict(eps=1e-6), residual_mult=0.5,
                 embedding=dict(scale=1.0), token_side=dict(dim=128))
 
 
@@ -764,9 +764,9 @@ def time_zogepel(widths: list[int], layers: int, steps: int, warmup: int, pk: di
         # the norms and gates around the sublayers, T rows: bytes moved over the measured copy bandwidth
         x, y = torch.randn(T, width, device="cuda"), torch.randn(T, width, device="cuda")
         gain = torch.ones(width, device="cuda")
-        ms = timed(lambda: ops.residual_out_norm(x, y, gain, 1e-6, bf, mult=0.7, scale=gain))
+        ms = timed(lambda: ops.residual_out_norm(x, y, gain, 1e-6, bf, mult=0.5, scale=gain))
         kern["residual_out_norm"] = {"ms": round(ms, 4), "hbm_frac": round(T * width * 14 / (ms * 1e-3) / bw, 3)}
-        ms = timed(lambda: ops.residual_out_norm(x, y, gain, 1e-6, bf, mult=0.7, scale=gain, halves=(y, gain, gain)))
+        ms = timed(lambda: ops.residual_out_norm(x, y, gain, 1e-6, bf, mult=0.5, scale=gain, halves=(y, gain, gain)))
         kern["residual_out_norm_two_halves"] = {"ms": round(ms, 4), "hbm_frac": round(T * width * 18 / (ms * 1e-3) / bw, 3)}
         ms = timed(lambda: ops.scaled_add_rms_norm(x, y, 1.0, gain, 1e-6, bf))
         kern["scaled_add_rms_norm"] = {"ms": round(ms, 4), "hbm_frac": round(T * width * 14 / (ms * 1e-3) / bw, 3)}

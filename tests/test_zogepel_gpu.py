@@ -34,7 +34,7 @@ def doubles(w, prefix=""):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("d", [72, 320, 1030])
+@pytest.mark.parametrize("d", [72, 328, 1030])
 def test_norm_on_the_sublayers_output(dtype, d):
     """x + mult * N(y) * gain * scale with the centred and the RMS norm, with and without a layer
     scale, with the sublayer's output given as two halves, and the norm alone on chosen rows."""
@@ -45,16 +45,16 @@ def test_norm_on_the_sublayers_output(dtype, d):
     T = 11
     gain, scale, ga, gb = (1 + 0.1 * torch.randn(d, generator=g) for _ in range(4))
     x, y, b = torch.randn(T, d, generator=g), 3 + 2 * torch.randn(T, d, generator=g), 0.1 * torch.randn(T, d, generator=g)
-    norm = build_part("norm", PartSpec("output_norm", dict(eps=EPS, mult=0.7, tensor="n", scale_tensor="s")), d)
+    norm = build_part("norm", PartSpec("output_norm", dict(eps=EPS, mult=0.6, tensor="n", scale_tensor="s")), d)
     norm.load({"n": gain.cuda(), "s": scale.cuda()})
     norm.bind_dtype(dtype)
     stream, copy = norm.add_forward(x.cuda(), y.cuda())
-    ref = x.double() + 0.7 * plain.layer_norm(y.double(), gain.double(), EPS) * scale.double()
+    ref = x.double() + 0.6 * plain.layer_norm(y.double(), gain.double(), EPS) * scale.double()
     check(stream, ref.float(), torch.float32, "stream after a centred norm")
     assert stream.dtype == torch.float32 and copy.dtype == dtype and torch.equal(copy.float(), stream.to(dtype).float())
     joined = 0.5 * (plain.rms_unit(y.double(), EPS) * ga.double() + plain.rms_unit(b.double(), EPS) * gb.double())
     stream, _ = norm.add_forward(x.cuda(), y.cuda(), (b.cuda(), ga.cuda(), gb.cuda()))
-    check(stream, (x.double() + 0.7 * plain.layer_norm(joined, gain.double(), EPS) * scale.double()).float(), torch.float32, "two halves")
+    check(stream, (x.double() + 0.6 * plain.layer_norm(joined, gain.double(), EPS) * scale.double()).float(), torch.float32, "two halves")
     plain_rms = ops.residual_out_norm(x.cuda(), y.cuda(), gain.cuda(), EPS, dtype, mult=1.3, centred=False)[0]
     check(plain_rms, (x.double() + 1.3 * plain.rms_unit(y.double(), EPS) * gain.double()).float(), torch.float32, "RMS form, no layer scale")
     rows = torch.tensor([7, 0, 3], dtype=torch.int32, device="cuda")
@@ -63,7 +63,7 @@ def test_norm_on_the_sublayers_output(dtype, d):
     check(last, plain.layer_norm(y.double(), gain.double(), EPS).float()[[7, 0, 3]], dtype, "the norm alone on chosen rows", 0.01)
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 384, 320), (8, 8192, 2048), (33, 100, 64), (200, 1024, 512), (600, 768, 256), (2048, 4096, 1024), (1024, 5000, 2048)])
+@pytest.mark.parametrize("M,N,K", [(1, 392, 328), (8, 8192, 2048), (33, 100, 64), (200, 1024, 512), (600, 768, 256), (2048, 4096, 1024), (1024, 5000, 2048)])
 def test_squared_relu_in_the_products_epilogue(M, N, K):
     """max(x W^T, 0)^2 from the tensor-core GEMMs' epilogues (few tokens with K cut and a reduction
     kernel, single SMs, pairs of SMs, a last round cut along K) against float64, rounded once."""
@@ -99,17 +99,17 @@ def test_output_norm_reading_a_products_partial_sums():
 
     g = torch.Generator().manual_seed(4)
     met = 0
-    for T, d, K in ((1, 256, 512), (5, 320, 1024), (8, 2048, 2048), (33, 256, 384)):
+    for T, d, K in ((1, 256, 512), (5, 336, 1024), (8, 2048, 2048), (33, 256, 392)):
         inner = (torch.randn(T, K, generator=g)).bfloat16().cuda()
         w = (torch.randn(d, K, generator=g) * K**-0.5).bfloat16().cuda()
         x = torch.randn(T, d, generator=g).cuda()
         gain, scale = ((1 + 0.1 * torch.randn(d, generator=g)).cuda() for _ in range(2))
         for centred, sc in ((True, scale), (False, None)):
-            whole = ops.residual_out_norm(x, ops.linear(inner, w, out_dtype=torch.float32), gain, EPS, torch.bfloat16, mult=0.7,
+            whole = ops.residual_out_norm(x, ops.linear(inner, w, out_dtype=torch.float32), gain, EPS, torch.bfloat16, mult=0.6,
                                           scale=sc, centred=centred)  # fmt: skip
             y = ops.linear_for_stream(inner, w)
             met += isinstance(y, PartialSums)
-            fused = ops.residual_out_norm(x, y, gain, EPS, torch.bfloat16, mult=0.7, scale=sc, centred=centred)
+            fused = ops.residual_out_norm(x, y, gain, EPS, torch.bfloat16, mult=0.6, scale=sc, centred=centred)
             what = f"{T} tokens, width {d}, K {K}, centred {centred}"
             assert float((whole[0] - fused[0]).abs().max() / whole[0].abs().max()) < 2e-6, what
             assert bool(((whole[1].float() - fused[1].float()).abs() <= 2.0**-7 * whole[1].float().abs() + 1e-30).all()), what
@@ -333,7 +333,7 @@ def test_attention_with_a_sink(dtype, H, KV, hd, bs, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("window,bs,hd", [(96, 16, 32), (7, 8, 32), (33, 16, 128), (16, 16, 64), (100, 16, 128), (250, 16, 128), (290, 16, 64)])
+@pytest.mark.parametrize("window,bs,hd", [(90, 16, 32), (7, 8, 32), (33, 16, 128), (16, 16, 64), (100, 16, 128), (250, 16, 128), (290, 16, 64)])
 def test_one_key_stands_out_at_the_windows_edges_and_the_sink_counts_once(dtype, window, bs, hd):
     """All keys are zero but one whose score is large; its value is e_1. For a query at position p
     the key at p - window + 1 is the last one seen and the key at p - window the first one not

@@ -52,7 +52,7 @@ ZOGEPEL_C = dict(
     architecture="Zogepel", vocab=640, width=256, residual_mult=0.5, norm=dict(eps=2e-6), embedding=dict(scale=8.0),
     token_side=dict(dim=24),
     layers=[
-        _mlstm(4, 128, 64, 12.0, 512),
+        _mlstm(4, 128, 64, 11.0, 512),
         _parallel(_left(8, 2, 64, 100, 0.2), _right(4, 64, 128, [0.9, 0.99, 0.999, 1.0], 100000.0, 32), 384),
         _parallel(_left(4, 1, 128, 33, 0.15), _right(3, 32, 64, [0.75, 0.95, 0.98], 500.0, 32), None),
         _mlstm(2, 64, 160, 8.0, 256),
