@@ -87,7 +87,7 @@ class LightningAttention(Mixer):
         rotary = self.position.fused_rotary() if self.position is not None else None
         table = None
         if rotary:  # the step's cosines and sines, made once for all layers that turn by these frequencies
-            key = f"rotary_table:{self.position.theta}:{rotary.rotary_dim}"
+            key = f"rotary_table:{getattr(self.position, 'theta', id(self.position))}:{rotary.rotary_dim}"
             if key not in ctx.plans:
                 ctx.plans[key] = ops.rotary_table(ctx.positions[: proj.shape[0]], rotary.inv_freq)
             table = ctx.plans[key]
